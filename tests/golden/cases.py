@@ -1,0 +1,30 @@
+"""The seeded cases behind the golden fixtures (shared by the generator and the tests)."""
+from pbs_attn_b200.synth import Workload
+
+# name -> (workload, seed, extra kwargs of the attention call, row stride of the stored output)
+CASES = {
+    # task configuration 1: the CPU op-level check
+    "op_check_fp32": (Workload("op_check_fp32", 1, 4, 1, 64, 2048, "fp32", 64, 256, 0.9, 1e4), 0, {}, 8),
+    # Llama-3.1-8B head shape, shortened sequence, with sink tokens
+    "llama_bf16_s4096": (Workload("llama_bf16_s4096", 1, 8, 2, 128, 4096, "bf16", 128, 256, 0.9, 5e5, sinks=4), 1, {}, 16),
+    "llama_bf16_t080": (Workload("llama_bf16_t080", 1, 4, 1, 128, 2048, "bf16", 128, 256, 0.8, 5e5, sinks=4), 2, {}, 8),
+    "llama_bf16_t095": (Workload("llama_bf16_t095", 1, 4, 1, 128, 2048, "bf16", 128, 256, 0.95, 5e5, sinks=4), 3, {}, 8),
+    # Qwen2.5-7B head shape (7 query heads per KV head), small blocks and segments
+    "qwen_bf16_bs64_seg128": (Workload("qwen_bf16_bs64_seg128", 1, 7, 1, 128, 2048, "bf16", 64, 128, 0.9, 1e6, density=0.08), 4, {}, 8),
+    "qwen_bf16_seg512": (Workload("qwen_bf16_seg512", 1, 7, 1, 128, 3072, "bf16", 128, 512, 0.9, 1e6, density=0.005), 5, {}, 8),
+    # ragged lengths: S % block_size != 0 and S % segment_size != 0
+    "ragged_fp32_s1000": (Workload("ragged_fp32_s1000", 1, 2, 2, 64, 1000, "fp32", 64, 256, 0.9, 1e4), 6, {}, 4),
+    "ragged_bf16_s1900": (Workload("ragged_bf16_s1900", 2, 4, 2, 128, 1900, "bf16", 128, 256, 0.9, 5e5, sinks=4), 7, {}, 8),
+    # batch 2, fp16
+    "batch2_fp16": (Workload("batch2_fp16", 2, 2, 1, 64, 1024, "fp16", 64, 256, 0.9, 1e4), 8, {}, 4),
+    # options
+    "no_first_block": (Workload("no_first_block", 1, 2, 1, 64, 1024, "fp32", 64, 256, 0.7, 1e4), 9,
+                       {"force_select_first_block": False}, 4),
+    "dense_int_threshold": (Workload("dense_int_threshold", 1, 2, 1, 64, 1024, "fp32", 64, 256, 1, 1e4), 10,
+                            {"force_select_first_block": False}, 4),
+    "max_pool": (Workload("max_pool", 1, 2, 1, 64, 1024, "bf16", 64, 256, 0.9, 1e4), 11,
+                 {"query_pool_mode": "max", "key_pool_mode": "max"}, 4),
+    "threshold_never_reached": (Workload("threshold_never_reached", 1, 2, 1, 64, 1024, "fp32", 64, 256, 1.5, 1e4), 12, {}, 4),
+    # q_len <= segment_size: the dense fallback
+    "short_dense": (Workload("short_dense", 1, 4, 2, 64, 200, "bf16", 64, 256, 0.9, 1e4), 13, {}, 1),
+}

@@ -1,0 +1,119 @@
+"""Generates tests/golden/*.npz by running the UNMODIFIED reference on seeded inputs.
+
+Run once, in a container that has the reference checked out (it is imported
+from REFERENCE_ROOT, default /root/reference, and is not needed afterwards):
+
+    python tests/golden/make_golden.py
+
+Per case two runs are stored: ``*_ref`` from the reference as it is (its sorts
+are non-stable: the order of tied items is implementation defined) and
+``*_stable`` from the same code with ``torch.sort`` / ``torch.argsort`` forced to
+``stable=True`` by a shim, which is the canonical tie-break the CUDA path and
+the oracle implement.  Inputs are regenerated from the seed by
+``pbs_attn_b200.synth.make_qkv``; their SHA-256 is stored so that a drift of the
+random generator is detected instead of silently changing the comparison.
+"""
+import contextlib
+import hashlib
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+
+
+def _import_reference():
+    """Import the reference's pbs_attn package, shadowing any same-named package of this repo."""
+    for name in [m for m in sys.modules if m == "pbs_attn" or m.startswith("pbs_attn.")]:
+        del sys.modules[name]
+    sys.path.insert(0, REFERENCE_ROOT)
+    try:
+        import pbs_attn.src.pbs as ref_pbs
+        assert os.path.abspath(ref_pbs.__file__).startswith(os.path.abspath(REFERENCE_ROOT)), ref_pbs.__file__
+    finally:
+        sys.path.remove(REFERENCE_ROOT)
+    return ref_pbs
+
+
+@contextlib.contextmanager
+def stable_sorts():
+    sort, argsort = torch.sort, torch.argsort
+
+    def s(x, *a, **k):
+        k["stable"] = True
+        return sort(x, *a, **k)
+
+    def a_(x, *a, **k):
+        k["stable"] = True
+        return argsort(x, *a, **k)
+
+    torch.sort, torch.argsort = s, a_
+    try:
+        yield
+    finally:
+        torch.sort, torch.argsort = sort, argsort
+
+
+def sha_inputs(*tensors) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        h.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+    return h.hexdigest()
+
+
+def raw(t: torch.Tensor) -> np.ndarray:
+    """bit pattern of a tensor as a numpy array (bf16/fp16 -> uint16, fp32 -> float32)."""
+    t = t.contiguous()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+def run_reference(ref_pbs, q, k, v, w, kwargs):
+    """One reference call plus its intermediates, obtained by calling its own stage functions."""
+    n_rep = w.q_heads // w.kv_heads
+    kr, vr = k.repeat_interleave(n_rep, dim=1), v.repeat_interleave(n_rep, dim=1)
+    out = ref_pbs.permuted_block_sparse_attn_fwd(q, kr, vr, w.block_size, w.segment_size, w.threshold,
+                                                 True, use_triton=False, **kwargs)
+    if w.seq_len <= w.segment_size:
+        return out, None, None, None
+    perm_k, idx = ref_pbs.apply_permutation(q, kr, w.block_size, w.segment_size)
+    qi = torch.arange(w.seq_len).view(1, 1, -1).expand(w.batch, w.q_heads, -1)
+    scores, mask, seg_mask = ref_pbs.permuted_block_selection(
+        q, perm_k, qi, idx, w.block_size, w.segment_size, threshold=w.threshold, causal=True, **kwargs)
+    mask = mask | seg_mask[None, None]
+    return out, idx, mask, scores
+
+
+def main():
+    sys.path.insert(0, ROOT)
+    from pbs_attn_b200.synth import make_qkv
+    sys.path.insert(0, HERE)
+    from cases import CASES
+    ref_pbs = _import_reference()
+    torch.set_num_threads(os.cpu_count() or 1)
+    for name, (w, seed, kwargs, stride) in CASES.items():
+        q, k, v = make_qkv(w, seed)
+        rec = {"inputs_sha256": np.array(sha_inputs(q, k, v)), "row_stride": np.array(stride)}
+        for tag, ctx in (("ref", contextlib.nullcontext()), ("stable", stable_sorts())):
+            with ctx:
+                out, idx, mask, scores = run_reference(ref_pbs, q, k, v, w, kwargs)
+            rec[f"out_{tag}"] = raw(out[:, :, ::stride, :])
+            if idx is not None:
+                rec[f"idx_{tag}"] = idx.to(torch.int32).numpy()
+                rec[f"mask_{tag}"] = np.packbits(mask.numpy(), axis=-1)
+                if tag == "stable":
+                    rec["scores"] = torch.nan_to_num(scores, nan=-1.0).numpy()
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **rec)
+        same = "idx_ref" not in rec or (np.array_equal(rec["idx_ref"], rec["idx_stable"]),
+                                         np.array_equal(rec["mask_ref"], rec["mask_stable"]))
+        print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB, ref==stable (idx, mask): {same}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,72 @@
+"""Pins the CPU oracle against outputs of the unmodified reference (tests/golden/*.npz)."""
+import numpy as np
+import pytest
+import torch
+
+from cases import CASES
+from oracle import pbs_oracle
+from parity import assert_close_out, golden_mask, golden_out, load_case
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_oracle_equals_stable_reference(name):
+    """stable=True oracle == reference run with stable sorts: bit-exact everywhere."""
+    w, kwargs, stride, (q, k, v), g = load_case(name)
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold,
+                                                  stable=True, **kwargs)
+    out = r.out[:, :, ::stride, :]
+    assert torch.equal(out.float(), golden_out(g, "stable", w.torch_dtype).float()) or \
+        np.array_equal(np.isnan(out.float().numpy()), np.isnan(golden_out(g, "stable", w.torch_dtype).float().numpy()))
+    if "idx_stable" in g:
+        nb = -(-w.seq_len // w.block_size)
+        assert np.array_equal(r.key_indices.numpy().astype(np.int32), g["idx_stable"])
+        assert torch.equal(r.block_mask, golden_mask(g, "stable", nb))
+        assert np.array_equal(torch.nan_to_num(r.block_scores, nan=-1.0).numpy(), g["scores"])
+    else:
+        assert r.key_indices is None
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_oracle_vs_unmodified_reference(name):
+    """Against the reference exactly as shipped (non-stable sorts): outputs within the
+    stated tolerance; permutation and mask equal except where its sort broke a tie
+    differently (the two reference runs themselves differ only there)."""
+    w, kwargs, stride, (q, k, v), g = load_case(name)
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold,
+                                                  stable=False, **kwargs)
+    assert_close_out(r.out[:, :, ::stride, :], golden_out(g, "ref", w.torch_dtype), w.torch_dtype, name)
+    if "idx_ref" in g:
+        nb = -(-w.seq_len // w.block_size)
+        assert np.array_equal(r.key_indices.numpy().astype(np.int32), g["idx_ref"])
+        assert torch.equal(r.block_mask, golden_mask(g, "ref", nb))
+
+
+def test_oracle_dense_threshold_is_causal_sdpa():
+    """threshold == int 1 without the forced first block selects every causal block, so the
+    result is dense causal attention (property of the reference, pbs.py:120-121)."""
+    w, kwargs, stride, (q, k, v), g = load_case("dense_int_threshold")
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, 1, **kwargs)
+    kr = k.repeat_interleave(w.q_heads // w.kv_heads, 1)
+    vr = v.repeat_interleave(w.q_heads // w.kv_heads, 1)
+    dense = torch.nn.functional.scaled_dot_product_attention(q, kr, vr, is_causal=True)
+    assert (r.out - dense).abs().max() < 1e-5
+
+
+def test_oracle_first_segment_rows_select_nothing_by_score():
+    w, kwargs, stride, (q, k, v), g = load_case("no_first_block")
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, **kwargs)
+    bps = w.segment_size // w.block_size
+    first = r.block_mask[:, :, :bps]
+    assert first[..., :bps].all() and not first[..., bps:].any()
+
+
+def test_oracle_threshold_never_reached_keeps_only_forced_blocks():
+    w, kwargs, stride, (q, k, v), g = load_case("threshold_never_reached")
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, **kwargs)
+    nb = r.block_mask.shape[-1]
+    bps = w.segment_size // w.block_size
+    qb = torch.arange(nb)[:, None]
+    kb = torch.arange(nb)[None, :]
+    same = (qb // bps) == (kb // bps)
+    forced = same[None, None] | pbs_oracle.first_token_blocks(r.key_indices, w.seq_len, w.block_size)
+    assert torch.equal(r.block_mask, forced.expand_as(r.block_mask))
