@@ -1,0 +1,173 @@
+/*
+ * pbs_b200.h -- C ABI of the B200 (sm_100a) PBS-Attn prefill library, libpbs_b200.so.
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and element strides, launches
+ * its kernels on the given CUDA stream and returns without synchronising.  Nothing
+ * here allocates: all scratch memory is passed in by the caller (sizes come from
+ * pbs_scratch_sizes).  Return value: 0 on success, a negative pbs_status_t on a
+ * rejected call (nothing was launched); pbs_last_error_string() describes the last
+ * rejection on the calling thread.
+ *
+ * "Replaces" lines cite the reference project's Python interface that each entry
+ * point stands in for (paths relative to the reference root, xinghaow99/pbs-attn).
+ *
+ * Tensors: q is (B, Hq, S, D), k and v are (B, Hkv, S, D) with Hkv dividing Hq; query
+ * head h reads KV head h / (Hq / Hkv) (the reference repeats K/V to Hq heads before
+ * its call, pbs_attn/patch/huggingface.py:209-211; passing the repeated tensors with
+ * Hkv == Hq is equally valid).  Strides are in ELEMENTS, order (b, h, s, d); the d
+ * stride must be 1, rows must start on 16-byte boundaries, head strides may be 0.
+ */
+#ifndef PBS_B200_H_
+#define PBS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { PBS_BF16 = 0, PBS_FP16 = 1, PBS_FP32 = 2 } pbs_dtype_t;
+typedef enum { PBS_POOL_MEAN = 0, PBS_POOL_MAX = 1 } pbs_pool_t;
+typedef enum { PBS_ATTN_AUTO = 0, PBS_ATTN_SIMT = 1, PBS_ATTN_TCGEN05 = 2 } pbs_attn_impl_t;
+
+typedef enum {
+  PBS_OK = 0,
+  PBS_ERR_SHAPE = -1,     /* unsupported or inconsistent sizes                         */
+  PBS_ERR_LAYOUT = -2,    /* stride / alignment the kernels cannot read                */
+  PBS_ERR_ARG = -3,       /* null pointer, bad enum                                    */
+  PBS_ERR_CUDA = -4,      /* a CUDA runtime / driver call failed                       */
+  PBS_ERR_UNSUPPORTED = -5 /* requested kernel cannot run this shape (e.g. tcgen05 path) */
+} pbs_status_t;
+
+/* Problem sizes shared by all entry points. */
+typedef struct {
+  int32_t batch;         /* B                                              */
+  int32_t q_heads;       /* Hq                                             */
+  int32_t kv_heads;      /* Hkv, divides Hq                                */
+  int32_t seq_len;       /* S (q_len == kv_len: prefill)                   */
+  int32_t head_dim;      /* D, multiple of 8, <= 256                       */
+  int32_t block_size;    /* selection granularity, multiple of 16, <= 256  */
+  int32_t segment_size;  /* permutation granularity, multiple of block_size */
+  int32_t dtype;         /* pbs_dtype_t of q, k, v and the output          */
+} pbs_shape_t;
+
+/* Element counts (NOT bytes) of every scratch buffer for a shape. */
+typedef struct {
+  int64_t logits;        /* dtype   : (B, Hq, block_size, L) last-block logits, L = (S / seg) * seg */
+  int64_t partials;      /* float2  : (B, Hq, L / 64, block_size) per-tile row max / sum            */
+  int64_t rowstats;      /* float2  : (B, Hq, block_size) row max and 1 / row sum                   */
+  int64_t importance;    /* float   : (B, Hq, L)                                                    */
+  int64_t key_indices;   /* int32   : (B, Hq, S)                                                    */
+  int64_t perm_kv;       /* dtype   : (B, Hq, S, D), once for K and once for V                      */
+  int64_t pooled;        /* dtype   : (B, Hq, nb, D), once for Q and once for K, nb = ceil(S / bs)  */
+  int64_t first_block;   /* int32   : (B, Hq)                                                       */
+  int64_t block_mask;    /* uint8   : (B, Hq, nb, nb)                                               */
+  int64_t tile_list;     /* uint32  : (B, Hq, ceil(S / 256), ceil(S / 128))                         */
+  int64_t tile_count;    /* int32   : (B, Hq, ceil(S / 256))                                        */
+  int64_t status;        /* int32   : 8 words, device-side error flags                              */
+} pbs_scratch_sizes_t;
+
+/* Device pointers of the scratch buffers, sized by pbs_scratch_sizes. */
+typedef struct {
+  void* logits;
+  void* partials;
+  void* rowstats;
+  float* importance;
+  int32_t* key_indices;
+  void* perm_k;
+  void* perm_v;
+  void* pooled_q;
+  void* pooled_k;
+  int32_t* first_block;
+  uint8_t* block_mask;
+  uint32_t* tile_list;
+  int32_t* tile_count;
+  int32_t* status;
+} pbs_scratch_t;
+
+/* Options of the whole-path call; mirrors the keyword arguments of
+ * permuted_block_sparse_attn_fwd (pbs_attn/src/pbs.py:132-146). */
+typedef struct {
+  const float* threshold_per_head; /* device, (Hq) floats, or NULL to use `threshold`        */
+  float threshold;                 /* cumulative-score threshold, compared in fp32           */
+  int32_t select_all;              /* 1: threshold was the Python int 1 -> every candidate   */
+  int32_t force_select_first_block;
+  int32_t query_pool_mode;         /* pbs_pool_t                                             */
+  int32_t key_pool_mode;           /* pbs_pool_t                                             */
+  int32_t attn_impl;               /* pbs_attn_impl_t                                        */
+} pbs_options_t;
+
+const char* pbs_last_error_string(void);
+int pbs_version(void);
+
+/* Validates the shape and fills the scratch element counts. */
+int pbs_scratch_sizes(const pbs_shape_t* shape, pbs_scratch_sizes_t* sizes);
+
+/* Stage 1a.  importance[b,h,j] = mean over the last block's queries of
+ * softmax_j(q . k_j / sqrt(D)) over the keys of the complete segments.
+ * Replaces pbs_attn/src/permute_states.py:44-50 (inside last_block_attn_sorting). */
+int pbs_key_importance(const pbs_shape_t* shape,
+                       const void* q, const int64_t q_strides[4],
+                       const void* k, const int64_t k_strides[4],
+                       void* logits, void* partials, void* rowstats,
+                       float* importance, void* stream);
+
+/* Stage 1b.  Stable descending sort of the importance inside each segment, gather of
+ * K and V rows into permuted order, block pooling of the permuted K, and the index of
+ * the permuted block that holds original token 0.
+ * Replaces pbs_attn/src/permute_states.py:52-83 (argsort + gather), pbs_attn/src/pbs.py:213-215
+ * (V gather), pbs_attn/src/utils.py:24-27 (key pooling), pbs_attn/src/pbs.py:10-25 (first token). */
+int pbs_segment_permute(const pbs_shape_t* shape, const float* importance,
+                        const void* k, const int64_t k_strides[4],
+                        const void* v, const int64_t v_strides[4],
+                        int32_t* key_indices, void* perm_k, void* perm_v,
+                        void* pooled_k, int32_t key_pool_mode, int32_t* first_block,
+                        void* stream);
+
+/* Stage 2a.  Block pooling of the queries.  Replaces pbs_attn/src/utils.py:18-21. */
+int pbs_pool_queries(const pbs_shape_t* shape, const void* q, const int64_t q_strides[4],
+                     void* pooled_q, int32_t query_pool_mode, void* stream);
+
+/* Stage 2b.  Pooled logits, fp32 softmax over the kv blocks of earlier segments,
+ * cumulative-threshold selection, then OR of the first-token block and of the q block's
+ * own segment.  block_mask is (B, Hq, nb, nb) bytes of 0/1.
+ * Replaces pbs_attn/src/utils.py:30-34 (block_pooled_attn), :38-86 (select_blocks),
+ * pbs_attn/src/pbs.py:95-127 (permuted_block_selection) and :209. */
+int pbs_select_blocks(const pbs_shape_t* shape, const void* pooled_q, const void* pooled_k,
+                      const int32_t* first_block, const pbs_options_t* options,
+                      uint8_t* block_mask, void* stream);
+
+/* Stage 3a.  Per 256-query group, the compact list of 128-key tiles that any of its
+ * query blocks selected (consumed by the tcgen05 attention kernel). */
+int pbs_build_tile_lists(const pbs_shape_t* shape, const uint8_t* block_mask,
+                         uint32_t* tile_list, int32_t* tile_count, void* stream);
+
+/* Stage 3b.  Block-sparse causal flash-attention forward over permuted K/V; the output is
+ * written in original token order with the given strides (queries are never permuted,
+ * pbs_attn/src/pbs.py:191-193, so the inverse permutation is the identity and is folded
+ * into the store).  Replaces the launch at pbs_attn/src/pbs.py:220-246 of the kernel
+ * pbs_attn/src/kernels/permuted_block_sparse_attention.py:134-311.
+ * status: 8 int32 words, zero on entry; word 0 becomes non-zero if a bounded device-side
+ * wait ran out (the output is then invalid). */
+int pbs_attn_fwd(const pbs_shape_t* shape,
+                 const void* q, const int64_t q_strides[4],
+                 const void* perm_k, const void* perm_v, const int32_t* key_indices,
+                 const uint8_t* block_mask, const uint32_t* tile_list, const int32_t* tile_count,
+                 void* out, const int64_t out_strides[4],
+                 int32_t attn_impl, int32_t* status, void* stream);
+
+/* Whole path: stages 1a..3b in order on one stream.  For S <= segment_size it runs dense
+ * causal attention like the reference (pbs_attn/src/pbs.py:175-182).
+ * Replaces permuted_block_sparse_attn_fwd, pbs_attn/src/pbs.py:132-257. */
+int pbs_prefill_fwd(const pbs_shape_t* shape,
+                    const void* q, const int64_t q_strides[4],
+                    const void* k, const int64_t k_strides[4],
+                    const void* v, const int64_t v_strides[4],
+                    void* out, const int64_t out_strides[4],
+                    const pbs_options_t* options, const pbs_scratch_t* scratch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PBS_B200_H_ */

@@ -1,0 +1,636 @@
+// Stage 3b, Blackwell kernel: block-sparse causal flash-attention forward on tcgen05 tensor cores.
+//
+// Math follows the reference's Triton kernel (pbs_attn/src/kernels/permuted_block_sparse_attention.py
+// :7-90,241-311): S = Q K^T accumulated in fp32, keys of the query tile's own segment are visible iff
+// their original position <= the query's, online softmax in base 2, P rounded to the input dtype
+// before P V, fp32 output accumulator, O / row-sum stored in the input dtype.
+//
+// Work item = 256 consecutive queries of one (b, h): two 128-row query tiles that share every K/V
+// tile staged in shared memory.  The item's tile list (built by tile_list_kernel) names the 128-key
+// tiles that either query tile selected.  A persistent CTA (one per SM) walks its items with
+// twelve warps in four roles:
+//   warp 0      TMA producer: Q tiles, then K and V tiles of the list into two 2-deep rings
+//   warp 1      MMA issuer:   S_i = Q_i K^T (SS, both operands K-major, 128B swizzle) and
+//                             O_i += P_i V  (TS: P read from TMEM, V MN-major from shared memory)
+//   warp 2      owns the TMEM allocation (all 512 columns: S0 S1 O0 O1, 128 columns each)
+//   warps 4-7   softmax of query tile 0: tcgen05.ld S, mask, row max / exp2 / row sum, P written
+//   warps 8-11  softmax of query tile 1  back over the first 64 columns of S as packed 16-bit
+//                             pairs; lazy rescale of O in TMEM; final O / l epilogue to global
+// The MMA issue order interleaves the two query tiles (PV0, QK0', PV1, QK1') so one tile's softmax
+// overlaps the other tile's MMAs.  Every wait on an mbarrier is bounded; when one runs out the CTA
+// raises a flag, all roles leave their loops, TMEM is freed and status[0] tells the host.
+#include <cuda.h>
+
+#include "pbs_common.cuh"
+
+namespace pbs {
+namespace {
+
+constexpr int kThreads = 384;
+constexpr int NK = 2;                     // K ring depth
+constexpr int NV = 2;                     // V ring depth
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.f;  // log2 units: O is rescaled only when the max grows by more
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// lbo / sbo are byte offsets (multiples of 16).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+template <int DT> struct PackP;
+template <> struct PackP<PBS_BF16> {
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct PackP<PBS_FP16> {
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Shared-memory plan
+// ---------------------------------------------------------------------------------------------
+struct Bars {
+  uint64_t q_full[2], q_empty[2];
+  uint64_t k_full[NK], k_empty[NK];
+  uint64_t v_full[NV], v_empty[NV];
+  uint64_t s_full[2], p_full[2], o_full[2];
+};
+
+struct Params {
+  const int32_t* idx;         // (B*Hq, S)
+  const uint32_t* list;       // (B*Hq, G, T)
+  const int32_t* count;       // (B*Hq, G)
+  void* out;
+  Strides os;
+  int Hq, S, G, T, n_items;
+  int bs;
+  float scale_log2e;
+  int32_t* status;
+};
+
+struct Ctl {
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+// Bounded wait: false when the CTA is aborting (this wait or another one ran out of time).
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (ctl->abort_flag) return false;
+      if (global_timer_ns() - t0 > 2000000000ull) {      // 2 s
+        ctl->abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+template <int D>
+struct Smem {
+  static constexpr int kTileBytes = 128 * D * 2;          // one 128-row tile
+  static constexpr int kQ = 0;                            // 2 tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;          // NK tiles
+  static constexpr int kV = kK + NK * kTileBytes;         // NV tiles
+  static constexpr int kIdx = kV + NV * kTileBytes;       // 8 warps x 128 int32
+  static constexpr int kBars = kIdx + 8 * 128 * 4;
+  static constexpr int kCtl = kBars + (int)sizeof(Bars);
+  static constexpr int kTotal = kCtl + (int)sizeof(Ctl) + 1024;   // + slack for 1024-byte alignment
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int DT, int D>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, Params p) {
+  using E = Elem<DT>;
+  using T = typename E::T;
+  using SM = Smem<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  Bars* bars = reinterpret_cast<Bars*>(smem + SM::kBars);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + SM::kCtl);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars->q_full[i]), 1);
+      mbar_init(smem_u32(&bars->q_empty[i]), 1);
+      mbar_init(smem_u32(&bars->s_full[i]), 1);
+      mbar_init(smem_u32(&bars->p_full[i]), 128);
+      mbar_init(smem_u32(&bars->o_full[i]), 1);
+    }
+    for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 1); }
+    for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 1); }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  const uint32_t tmem_S[2] = {tmem + 0u, tmem + 128u};
+  const uint32_t tmem_O[2] = {tmem + 256u, tmem + 384u};
+
+  constexpr int KH = D / 64;                              // 64-column (128-byte) slabs per tile row
+  constexpr uint32_t kSlab = 128 * 128;                   // bytes of one 128-row slab
+  constexpr uint32_t kTile = SM::kTileBytes;
+  // instruction descriptors: fp32 accumulate, A/B = bf16 or fp16, M = 128
+  constexpr uint32_t kFmt = (DT == PBS_BF16) ? 1u : 0u;
+  constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+  constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | (((uint32_t)D >> 3) << 17) | ((128u >> 4) << 24);
+
+  if (warp == 0) {
+    // =========================================================================== TMA producer
+    if (lane == 0) {
+      uint32_t kc = 0, vc = 0, qc[2] = {0, 0};
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        const int bh = item / p.G, g = p.G - 1 - item % p.G;
+        const int b = bh / p.Hq, h = bh % p.Hq;
+        for (int i = 0; i < 2 && ok; ++i) {
+          const int r0 = g * 256 + i * 128;
+          if (r0 >= p.S) continue;
+          ok = wait_bar(smem_u32(&bars->q_empty[i]), (qc[i] & 1u) ^ 1u, ctl, p.status, 1);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&bars->q_full[i]);
+          mbar_expect_tx(bar, kTile);
+          for (int kh = 0; kh < KH; ++kh)
+            tma_load_4d(sbase + SM::kQ + i * kTile + kh * kSlab, &map_q, bar, kh * 64, r0, h, b);
+          ++qc[i];
+        }
+        const int n = p.count[(int64_t)bh * p.G + g];
+        const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
+        for (int e = 0; e < n && ok; ++e) {
+          const int t = (int)(lst[e] & 0xFFFFu);
+          {
+            const uint32_t s = kc % NK;
+            ok = wait_bar(smem_u32(&bars->k_empty[s]), ((kc / NK) & 1u) ^ 1u, ctl, p.status, 2);
+            if (!ok) break;
+            const uint32_t bar = smem_u32(&bars->k_full[s]);
+            mbar_expect_tx(bar, kTile);
+            for (int kh = 0; kh < KH; ++kh)
+              tma_load_3d(sbase + SM::kK + s * kTile + kh * kSlab, &map_k, bar, kh * 64, t * 128, bh);
+            ++kc;
+          }
+          {
+            const uint32_t s = vc % NV;
+            ok = wait_bar(smem_u32(&bars->v_empty[s]), ((vc / NV) & 1u) ^ 1u, ctl, p.status, 3);
+            if (!ok) break;
+            const uint32_t bar = smem_u32(&bars->v_full[s]);
+            mbar_expect_tx(bar, kTile);
+            for (int kh = 0; kh < KH; ++kh)
+              tma_load_3d(sbase + SM::kV + s * kTile + kh * kSlab, &map_v, bar, kh * 64, t * 128, bh);
+            ++vc;
+          }
+        }
+      }
+      if (!ok) __nanosleep(200000);                       // let copies in flight land before teardown
+    }
+  } else if (warp == 1) {
+    // =========================================================================== MMA issuer
+    if (lane == 0) {
+      uint32_t kc = 0, vc = 0, qc[2] = {0, 0}, pc[2] = {0, 0};
+      bool ok = true;
+
+      auto issue_qk = [&](int i, uint32_t kstage) {
+        const uint32_t a0 = sbase + SM::kQ + i * kTile, b0 = sbase + SM::kK + kstage * kTile;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * kSlab + (ks & 3) * 32;
+          mma_ss(tmem_S[i], smem_desc(a0 + off, 16, 1024), smem_desc(b0 + off, 16, 1024), kIdescQK, ks > 0);
+        }
+        tc_commit(smem_u32(&bars->s_full[i]));
+      };
+      auto issue_pv = [&](int i, uint32_t vstage, bool accumulate) {
+        const uint32_t b0 = sbase + SM::kV + vstage * kTile;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)                    // 128 keys, 16 per instruction
+          mma_ts(tmem_O[i], tmem_S[i] + ks * 8, smem_desc(b0 + ks * 2048, kSlab, 1024), kIdescPV, (accumulate || ks > 0));
+        tc_commit(smem_u32(&bars->o_full[i]));
+      };
+
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        const int bh = item / p.G, g = p.G - 1 - item % p.G;
+        const int n = p.count[(int64_t)bh * p.G + g];
+        const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
+        bool have[2];
+        for (int i = 0; i < 2; ++i) {
+          have[i] = g * 256 + i * 128 < p.S;
+          if (have[i] && ok) { ok = wait_bar(smem_u32(&bars->q_full[i]), qc[i] & 1u, ctl, p.status, 4); ++qc[i]; }
+        }
+        if (!ok) break;
+        bool started[2] = {false, false};                 // O_i holds a partial sum of this item
+        uint32_t cur = n > 0 ? lst[0] : 0u;
+        if (n > 0) {
+          const uint32_t s = kc % NK;
+          ok = wait_bar(smem_u32(&bars->k_full[s]), (kc / NK) & 1u, ctl, p.status, 5);
+          if (!ok) break;
+          tc_fence_after();
+          for (int i = 0; i < 2; ++i)
+            if (cur & (1u << (16 + i))) issue_qk(i, s);
+          tc_commit(smem_u32(&bars->k_empty[s]));
+          ++kc;
+        }
+        for (int e = 0; e < n && ok; ++e) {
+          const uint32_t nxt = (e + 1 < n) ? lst[e + 1] : 0u;
+          const uint32_t vs = vc % NV;
+          ok = wait_bar(smem_u32(&bars->v_full[vs]), (vc / NV) & 1u, ctl, p.status, 6);
+          if (!ok) break;
+          const uint32_t ks = kc % NK;
+          bool k_ready = false;
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (cur & (1u << (16 + i))) {
+              ok = wait_bar(smem_u32(&bars->p_full[i]), pc[i] & 1u, ctl, p.status, 7);
+              if (!ok) break;
+              ++pc[i];
+              tc_fence_after();
+              issue_pv(i, vs, started[i]);
+              started[i] = true;
+            }
+            if (nxt & (1u << (16 + i))) {
+              if (!k_ready) {
+                ok = wait_bar(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
+                if (!ok) break;
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_qk(i, ks);
+            }
+          }
+          if (!ok) break;
+          tc_commit(smem_u32(&bars->v_empty[vs]));
+          ++vc;
+          if (nxt) { tc_commit(smem_u32(&bars->k_empty[ks])); ++kc; }
+          cur = nxt;
+        }
+        if (!ok) break;
+        for (int i = 0; i < 2; ++i)
+          if (have[i]) tc_commit(smem_u32(&bars->q_empty[i]));
+      }
+    }
+  } else if (warp >= 4) {
+    // =========================================================================== softmax + epilogue
+    const int i = (warp - 4) >> 2;                         // query tile of this warpgroup
+    const int wq = warp & 3;                               // TMEM lane quarter of this warp
+    const int row = wq * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
+    int32_t* kidx = reinterpret_cast<int32_t*>(smem + SM::kIdx) + (warp - 4) * 128;
+    const uint32_t bar_s = smem_u32(&bars->s_full[i]), bar_p = smem_u32(&bars->p_full[i]), bar_o = smem_u32(&bars->o_full[i]);
+    uint32_t sc = 0;                                       // softmax steps done = PVs requested so far
+    bool ok = true;
+
+    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      const int bh = item / p.G, g = p.G - 1 - item % p.G;
+      const int r0 = g * 256 + i * 128;
+      if (r0 >= p.S) continue;
+      const int b = bh / p.Hq, h = bh % p.Hq;
+      const int qpos = r0 + row;
+      const int n = p.count[(int64_t)bh * p.G + g];
+      const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
+      const int32_t* ibase = p.idx + (int64_t)bh * p.S;
+      float m_used = -CUDART_INF_F;                        // scaled (log2) max the exponents refer to
+      float l = 0.f;
+      uint32_t steps = 0;                                  // softmax steps of this item
+
+      for (int e = 0; e < n && ok; ++e) {
+        const uint32_t ent = lst[e];
+        if (!(ent & (1u << (16 + i)))) continue;
+        const int t = (int)(ent & 0xFFFFu);
+        const bool elem_mask = ent & (1u << (18 + i));
+        const uint32_t bits = (ent >> (20 + 4 * i)) & 0xFu;
+        if (elem_mask) {
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int kp = t * 128 + c * 32 + lane;
+            kidx[c * 32 + lane] = kp < p.S ? ibase[kp] : 0x7fffffff;
+          }
+          __syncwarp();
+        }
+        ok = __all_sync(0xffffffffu, wait_bar(bar_s, sc & 1u, ctl, p.status, 9));
+        if (!ok) break;
+        tc_fence_after();
+
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + c * 32, sr[c]);
+        tmem_wait_ld();
+        float* s = reinterpret_cast<float*>(&sr[0][0]);
+
+        if (elem_mask) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            if (kidx[c] > qpos) s[c] = -CUDART_INF_F;
+        }
+        if (p.bs == 64) {                                  // 64x64 sub-blocks that were not selected
+          const int qi = row >> 6;
+#pragma unroll
+          for (int ki = 0; ki < 2; ++ki)
+            if (!((bits >> (2 * qi + ki)) & 1u)) {
+#pragma unroll
+              for (int c = 0; c < 64; ++c) s[ki * 64 + c] = -CUDART_INF_F;
+            }
+        }
+        float mt = s[0];
+#pragma unroll
+        for (int c = 1; c < 128; ++c) mt = fmaxf(mt, s[c]);
+        mt *= p.scale_log2e;
+
+        float alpha = 1.f;
+        if (mt > m_used + kRescaleThreshold) {             // also the first finite maximum
+          alpha = exp2f(m_used - mt);                      // 0 when m_used is -inf
+          m_used = mt;
+          l *= alpha;
+        }
+        const bool rescale = steps > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+        const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+        float lsum = 0.f;
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const float p0 = exp2f(fmaf(s[2 * c], p.scale_log2e, -m_eff));
+          const float p1 = exp2f(fmaf(s[2 * c + 1], p.scale_log2e, -m_eff));
+          lsum += p0 + p1;
+          pk[c >> 5][c & 31] = PackP<DT>::pack(p0, p1);
+        }
+        l += lsum;
+        tmem_st32(tmem_S[i] + lane_off, pk[0]);
+        tmem_st32(tmem_S[i] + lane_off + 32, pk[1]);
+
+        if (rescale) {
+          // O_i holds the sum up to the previous step: wait for that PV, then scale in place
+          ok = __all_sync(0xffffffffu, wait_bar(bar_o, (sc - 1u) & 1u, ctl, p.status, 10));
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_O[i] + lane_off + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st32(tmem_O[i] + lane_off + c * 32, o);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p);
+        ++sc;
+        ++steps;
+      }
+      if (!ok) break;
+
+      // epilogue: O / l in the input dtype, original token order (queries are not permuted)
+      if (steps > 0) {
+        ok = __all_sync(0xffffffffu, wait_bar(bar_o, (sc - 1u) & 1u, ctl, p.status, 11));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)qpos * p.os.s;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (steps > 0) {
+          tmem_ld32(tmem_O[i] + lane_off + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (qpos < p.S) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 w;
+            w.x = PackP<DT>::pack(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+            w.y = PackP<DT>::pack(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+            w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+            w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + j * 8) = w;
+          }
+        }
+      }
+      // the next item's first P V overwrites O_i: order our TMEM reads before the arrive that lets it go
+      tc_fence_before();
+    }
+  }
+
+  // =============================================================================== teardown
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+int make_map(CUtensorMap* map, int dt, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PBS_ERR_CUDA; }
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dt == PBS_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                  const_cast<void*>(base), dims, strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", (int)r); return PBS_ERR_CUDA; }
+  return PBS_OK;
+}
+
+template <int DT, int D>
+int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void* pv, const int32_t* idx,
+           const uint32_t* list, const int32_t* count, void* out, Strides os, int32_t* status, cudaStream_t st) {
+  CUtensorMap mq, mk, mv;
+  const cuuint64_t e = 2;
+  {
+    // q: (D, S, Hq, B) with the caller's strides; size-1 dims get a harmless stride
+    cuuint64_t dims[4] = {(cuuint64_t)d.D, (cuuint64_t)d.S, (cuuint64_t)d.Hq, (cuuint64_t)d.B};
+    cuuint64_t row = (cuuint64_t)qs.s * e;
+    cuuint64_t sh = d.Hq > 1 ? (cuuint64_t)qs.h * e : row * d.S;
+    cuuint64_t sb = d.B > 1 ? (cuuint64_t)qs.b * e : (d.Hq > 1 ? sh * d.Hq : row * d.S);
+    if (sh == 0 || sb == 0) { set_error("q: zero head/batch stride is not supported by the tcgen05 kernel"); return PBS_ERR_LAYOUT; }
+    cuuint64_t strides[3] = {row, sh, sb};
+    int rc = make_map(&mq, DT, q, 4, dims, strides);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)d.D, (cuuint64_t)d.S, (cuuint64_t)d.B * d.Hq};
+    cuuint64_t strides[2] = {(cuuint64_t)d.D * e, (cuuint64_t)d.S * d.D * e};
+    int rc = make_map(&mk, DT, pk, 3, dims, strides);
+    if (rc) return rc;
+    rc = make_map(&mv, DT, pv, 3, dims, strides);
+    if (rc) return rc;
+  }
+  Params p;
+  p.idx = idx; p.list = list; p.count = count; p.out = out; p.os = os;
+  p.Hq = d.Hq; p.S = d.S; p.G = (d.S + 255) / 256; p.T = (d.S + 127) / 128;
+  p.n_items = d.B * d.Hq * p.G;
+  p.bs = d.bs;
+  p.scale_log2e = (float)(1.4426950408889634 / sqrt((double)d.D));
+  p.status = status;
+
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  auto kern = attn_tc_kernel<DT, D>;
+  const int smem = Smem<D>::kTotal;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (ce != cudaSuccess) return cuda_fail(ce, "attn_tc_kernel smem attribute");
+  const int grid = p.n_items < sm_count ? p.n_items : sm_count;
+  kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
+  PBS_CUDA_CHECK_LAUNCH("attn_tc_kernel");
+  return PBS_OK;
+}
+
+}  // namespace
+
+bool attn_tc_supported(const Dims& d, int dt) {
+  return (dt == PBS_BF16 || dt == PBS_FP16) && (d.D == 64 || d.D == 128) && (d.bs == 64 || d.bs == 128) &&
+         d.seg % 128 == 0 && (d.S + 127) / 128 <= 0xFFFF;
+}
+
+int launch_attn_tc(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,
+                   const int32_t* idx, const uint32_t* list, const int32_t* count, void* out, Strides os,
+                   int32_t* status, cudaStream_t st) {
+  if (dt == PBS_BF16) {
+    if (d.D == 128) return run_tc<PBS_BF16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+    return run_tc<PBS_BF16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+  }
+  if (d.D == 128) return run_tc<PBS_FP16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+  return run_tc<PBS_FP16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+}
+
+}  // namespace pbs

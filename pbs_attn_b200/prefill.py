@@ -1,0 +1,229 @@
+"""Host side of the prefill path: shapes, scratch memory and the calls into libpbs_b200.so.
+
+``permuted_block_sparse_attn_fwd`` has the signature and argument meaning of the
+reference's function of the same name (pbs_attn/src/pbs.py:132-146).  PyTorch is used
+for device memory and streams only; all arithmetic happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+from typing import Optional, Union
+
+import torch
+
+from . import _cabi
+
+_DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.FP16, torch.float32: _cabi.FP32}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _strides(t: torch.Tensor):
+    return _cabi.Strides4(*t.stride())
+
+
+def _readable(t: torch.Tensor) -> torch.Tensor:
+    """Returns ``t`` if the kernels can read it in place (unit head-dim stride, 16-byte aligned
+    rows), else a contiguous copy."""
+    e = t.element_size()
+    ok = (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and t.stride(2) > 0
+          and all((s * e) % 16 == 0 and s >= 0 for s in t.stride()[:3]))
+    return t if ok else t.contiguous()
+
+
+class Plan:
+    """Shape, scratch buffers and stage calls for one (shape, device).
+
+    Scratch lives in torch tensors (the library never allocates).  The stage methods map
+    one-to-one onto the C entry points; ``run`` is the whole path.
+    """
+
+    def __init__(self, batch, q_heads, kv_heads, seq_len, head_dim, block_size, segment_size,
+                 dtype: torch.dtype, device):
+        if dtype not in _DTYPES:
+            raise TypeError(f"unsupported dtype {dtype}: need bfloat16, float16 or float32")
+        self.lib = _cabi.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
+        self.dtype = dtype
+        self.shape = _cabi.Shape(batch, q_heads, kv_heads, seq_len, head_dim, block_size, segment_size, _DTYPES[dtype])
+        sizes = _cabi.ScratchSizes()
+        _cabi.check(self.lib.pbs_scratch_sizes(C.byref(self.shape), C.byref(sizes)), "pbs_scratch_sizes")
+        self.dense = seq_len <= segment_size
+        self.nb = -(-seq_len // block_size)
+        self.n_complete = (seq_len // segment_size) * segment_size
+        dev = self.device
+
+        def buf(n, dt):
+            return torch.empty(max(int(n), 1), dtype=dt, device=dev)
+
+        B, H, S, D = batch, q_heads, seq_len, head_dim
+        self.logits = buf(0 if self.dense else sizes.logits, dtype)
+        self.partials = buf(0 if self.dense else 2 * sizes.partials, torch.float32)
+        self.rowstats = buf(2 * sizes.rowstats, torch.float32)
+        self.importance = buf(sizes.importance, torch.float32)
+        self.key_indices = buf(sizes.key_indices, torch.int32).view(B, H, S)
+        self.perm_k = buf(sizes.perm_kv, dtype).view(B, H, S, D)
+        self.perm_v = buf(sizes.perm_kv, dtype).view(B, H, S, D)
+        self.pooled_q = buf(sizes.pooled, dtype).view(B, H, self.nb, D)
+        self.pooled_k = buf(sizes.pooled, dtype).view(B, H, self.nb, D)
+        self.first_block = torch.zeros(max(int(sizes.first_block), 1), dtype=torch.int32, device=dev)
+        self.block_mask = buf(sizes.block_mask, torch.uint8).view(B, H, self.nb, self.nb)
+        self.tile_list = buf(sizes.tile_list, torch.int32)
+        self.tile_count = buf(sizes.tile_count, torch.int32)
+        self.status = torch.zeros(int(sizes.status), dtype=torch.int32, device=dev)
+        self.scratch = _cabi.Scratch(*[t.data_ptr() for t in (
+            self.logits, self.partials, self.rowstats, self.importance, self.key_indices, self.perm_k,
+            self.perm_v, self.pooled_q, self.pooled_k, self.first_block, self.block_mask, self.tile_list,
+            self.tile_count, self.status)])
+        self._thr_dev = None
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def options(self, threshold, force_select_first_block=True, query_pool_mode="mean", key_pool_mode="mean",
+                attn_impl="auto") -> _cabi.Options:
+        for m in (query_pool_mode, key_pool_mode):
+            if m not in _cabi.POOL:
+                raise ValueError(f"Invalid pool mode: {m}")
+        thr_ptr, thr, select_all = None, 0.0, 0
+        if isinstance(threshold, torch.Tensor):
+            self._thr_dev = threshold.detach().to(device=self.device, dtype=torch.float32).reshape(-1).contiguous()
+            if self._thr_dev.numel() != self.shape.q_heads:
+                raise ValueError("a tensor threshold must hold one value per query head")
+            thr_ptr = self._thr_dev.data_ptr()
+        elif isinstance(threshold, int) and not isinstance(threshold, bool) and threshold == 1:
+            select_all = 1          # the reference takes every candidate block for the int 1
+        else:
+            thr = float(threshold)
+        return _cabi.Options(thr_ptr, thr, select_all, int(bool(force_select_first_block)),
+                             _cabi.POOL[query_pool_mode], _cabi.POOL[key_pool_mode], _cabi.ATTN_IMPL[attn_impl])
+
+    def check_status(self):
+        """Synchronises and raises if a kernel reported a device-side error."""
+        st = self.status.cpu()
+        if int(st[0]) != 0:
+            raise _cabi.PbsError(f"device-side error flags {st.tolist()}: a bounded wait in the attention kernel ran out")
+
+    # ------------------------------------------------------------------ stages
+    def key_importance(self, q, k):
+        _cabi.check(self.lib.pbs_key_importance(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                                _ptr(self.logits), _ptr(self.partials), _ptr(self.rowstats),
+                                                _ptr(self.importance), self._stream()), "pbs_key_importance")
+        return self.importance[: self.shape.batch * self.shape.q_heads * self.n_complete].view(
+            self.shape.batch, self.shape.q_heads, self.n_complete)
+
+    def segment_permute(self, k, v, key_pool_mode="mean", identity=False):
+        imp = None if identity else _ptr(self.importance)
+        _cabi.check(self.lib.pbs_segment_permute(C.byref(self.shape), imp, _ptr(k), _strides(k), _ptr(v), _strides(v),
+                                                 _ptr(self.key_indices), _ptr(self.perm_k), _ptr(self.perm_v),
+                                                 _ptr(self.pooled_k), _cabi.POOL[key_pool_mode],
+                                                 _ptr(self.first_block), self._stream()), "pbs_segment_permute")
+
+    def pool_queries(self, q, query_pool_mode="mean"):
+        _cabi.check(self.lib.pbs_pool_queries(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.pooled_q),
+                                              _cabi.POOL[query_pool_mode], self._stream()), "pbs_pool_queries")
+
+    def select_blocks(self, opt: _cabi.Options):
+        _cabi.check(self.lib.pbs_select_blocks(C.byref(self.shape), _ptr(self.pooled_q), _ptr(self.pooled_k),
+                                               _ptr(self.first_block), C.byref(opt), _ptr(self.block_mask),
+                                               self._stream()), "pbs_select_blocks")
+
+    def build_tile_lists(self):
+        _cabi.check(self.lib.pbs_build_tile_lists(C.byref(self.shape), _ptr(self.block_mask), _ptr(self.tile_list),
+                                                  _ptr(self.tile_count), self._stream()), "pbs_build_tile_lists")
+
+    def attn_fwd(self, q, out, attn_impl="auto"):
+        self.status.zero_()
+        _cabi.check(self.lib.pbs_attn_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.perm_k), _ptr(self.perm_v),
+                                          _ptr(self.key_indices), _ptr(self.block_mask), _ptr(self.tile_list),
+                                          _ptr(self.tile_count), _ptr(out), _strides(out), _cabi.ATTN_IMPL[attn_impl],
+                                          _ptr(self.status), self._stream()), "pbs_attn_fwd")
+
+    # ------------------------------------------------------------------ whole path
+    def run(self, q, k, v, out, opt: _cabi.Options):
+        _cabi.check(self.lib.pbs_prefill_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                             _ptr(v), _strides(v), _ptr(out), _strides(out), C.byref(opt),
+                                             C.byref(self.scratch), self._stream()), "pbs_prefill_fwd")
+        return out
+
+
+_PLANS: dict = {}
+_MAX_PLANS = 2
+
+
+def get_plan(q: torch.Tensor, kv_heads: int, block_size: int, segment_size: int) -> Plan:
+    """Scratch is reused between calls of the same shape on the same device (e.g. the layers
+    of one model); at most two shapes stay cached."""
+    B, Hq, S, D = q.shape
+    key = (B, Hq, kv_heads, S, D, block_size, segment_size, q.dtype, q.device.index)
+    plan = _PLANS.get(key)
+    if plan is None:
+        while len(_PLANS) >= _MAX_PLANS:
+            _PLANS.pop(next(iter(_PLANS)))
+        plan = _PLANS[key] = Plan(B, Hq, kv_heads, S, D, block_size, segment_size, q.dtype, q.device)
+    return plan
+
+
+def release_plans():
+    _PLANS.clear()
+
+
+def permuted_block_sparse_attn_fwd(
+    query_states: torch.Tensor,
+    key_states: torch.Tensor,
+    value_states: torch.Tensor,
+    block_size: int,
+    segment_size: int,
+    threshold: Union[float, torch.Tensor],
+    causal: bool,
+    force_select_first_block: bool = True,
+    use_triton: bool = True,
+    query_pool_mode: str = "mean",
+    key_pool_mode: str = "mean",
+    attn_impl: str = "auto",
+    intermediates: Optional[dict] = None,
+):
+    """Permuted block-sparse attention forward (prefill, causal) on the CUDA library.
+
+    Same arguments and result as the reference (pbs_attn/src/pbs.py:132-257): q is
+    (B, Hq, S, D); the result has q's shape, dtype and memory layout, in original token
+    order.  Differences, all additive:
+      * k/v may have Hkv < Hq heads (Hkv divides Hq); query head h uses KV head
+        h // (Hq // Hkv), which equals the reference result on ``repeat_kv``-ed tensors;
+      * ``use_triton`` is accepted and ignored (there is one backend);
+      * ``attn_impl`` picks the attention kernel ("auto", "tcgen05", "simt");
+      * ``intermediates``: a dict that receives the permutation, block mask and plan
+        (used by the parity tests).
+    Runs on the current CUDA stream without synchronising.
+    """
+    batch_size, num_q_heads, q_len, head_dim = query_states.shape
+    _, num_kv_heads, kv_len, _ = key_states.shape
+    assert num_q_heads % num_kv_heads == 0
+    assert causal
+    assert q_len == kv_len
+    assert value_states.shape == key_states.shape
+    if not query_states.is_cuda:
+        raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
+    assert segment_size % block_size == 0, "segment_size must be a multiple of block_size"
+
+    q = _readable(query_states)
+    k = _readable(key_states)
+    v = _readable(value_states)
+    plan = get_plan(q, num_kv_heads, block_size, segment_size)
+    opt = plan.options(threshold, force_select_first_block, query_pool_mode, key_pool_mode, attn_impl)
+    out = torch.empty_like(q)
+    plan.run(q, k, v, out, opt)
+    if intermediates is not None:
+        intermediates["plan"] = plan
+        intermediates["key_indices"] = plan.key_indices
+        intermediates["block_mask"] = plan.block_mask
+    if os.environ.get("PBS_B200_CHECK_STATUS") == "1":
+        plan.check_status()
+    return out
