@@ -1,0 +1,382 @@
+"""Benchmark of the PBS-Attn prefill attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--seq-len S] [--threshold T]
+
+One step = one permuted_block_sparse_attn_fwd call (all stages) on the Llama-3.1-8B head shape at
+131072 tokens (32 query / 8 KV heads, head_dim 128, bf16, block 128, segment 256, threshold 0.9,
+seeded synthetic Q/K/V with planted heavy-hitter keys, sinks and RoPE).  With N > 1 the KV-head
+groups are sharded over the ranks (strong scaling: the total work is fixed) and the step ends with
+the NCCL all-gather of the outputs.  Rank 0 prints one JSON line.
+
+  value      selected-block TFLOP/s (4 * bs^2 * D per selected block) of the whole job, inputs
+             resident in HBM, device time by CUDA events, max over ranks
+  e2e        the same metric through the public API with HOST (pinned) q/k/v copied to the device
+             and the output copied back inside the timed region
+  roofline   the attention kernel alone: selected-block FLOPs / its event-timed duration, against the
+             measured bf16 tensor peak (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (a port of the reference's PyTorch path) on a bounded sample
+
+--impl reference times that CPU port on the host cores for the same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from pbs_attn_b200.synth import WORKLOADS, Workload, make_qkv  # noqa: E402
+
+METRIC = "prefill_attn_selected_block_tflops"
+UNIT = "TFLOP/s"
+CPU_SAMPLE = dict(q_heads=4, kv_heads=1, seq_len=32768)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_burst": p["bf16_tflops"],
+                "bf16_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_burst": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def selected_flops(n_selected_blocks: float, w: Workload) -> float:
+    return 4.0 * w.block_size * w.block_size * w.head_dim * n_selected_blocks
+
+
+def dense_equiv_flops(w: Workload, q_heads: int) -> float:
+    return 2.0 * w.batch * q_heads * float(w.seq_len) ** 2 * w.head_dim
+
+
+class ClockSampler:
+    """nvidia-smi in the background while the timed region runs (read-only queries)."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 8:
+                continue
+            try:
+                sm.append(float(c[1]))
+                smax = max(smax, float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.file.close()
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(sm)[len(sm) // 4:]        # drop the idle quarter at the edges of the region
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_port_run(w: Workload, seed: int):
+    """One run of the CPU oracle on ``w``; returns (seconds, selected-block FLOPs)."""
+    from oracle import pbs_oracle
+    q, k, v = make_qkv(w, seed)
+    t = time.perf_counter()
+    r = pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, stable=False)
+    dt = time.perf_counter() - t
+    n_sel = float(r.block_mask.sum()) if r.block_mask is not None else 0.0
+    return dt, selected_flops(n_sel, w)
+
+
+def sample_workload(w: Workload) -> Workload:
+    s = dict(CPU_SAMPLE)
+    s["seq_len"] = min(s["seq_len"], w.seq_len)
+    s["kv_heads"] = 1
+    s["q_heads"] = w.q_heads // w.kv_heads
+    return w.with_(**s)
+
+
+def sample_text(ws: Workload) -> str:
+    return (f"{ws.q_heads} query heads / {ws.kv_heads} KV head of the workload at seq_len {ws.seq_len} "
+            f"(one full call of the CPU port per step)")
+
+
+def config_dict(w: Workload, world: int, extra=None):
+    c = {"workload": w.name, "batch": w.batch, "q_heads": w.q_heads, "kv_heads": w.kv_heads,
+         "head_dim": w.head_dim, "seq_len": w.seq_len, "block_size": w.block_size,
+         "segment_size": w.segment_size, "threshold": w.threshold, "rope_theta": w.rope_theta,
+         "hot_key_density": w.density, "sinks": w.sinks,
+         "parallelism": f"kv-head groups sharded over {world} GPU(s), outputs all-gathered" if world > 1 else "single GPU",
+         "l2": "inputs_exceed_l2"}
+    if extra:
+        c.update(extra)
+    return c
+
+
+# ------------------------------------------------------------------------------------ reference arm
+def run_reference(args, w: Workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    ws = sample_workload(w)
+    for i in range(args.warmup):
+        if i == 0:
+            cpu_port_run(ws, args.seed)          # one warm-up call is enough for a CPU path
+    times, fl = [], 0.0
+    for _ in range(args.steps):
+        dt, fl = cpu_port_run(ws, args.seed)
+        times.append(dt)
+    total = sum(times)
+    val = fl * len(times) / total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": config_dict(w, 1, {"measured_on": "bounded sample, see cpu_baseline.sample"}),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample_text(ws)},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------ our arm
+def run_ours(args, w: Workload):
+    import torch.distributed as dist
+    from pbs_attn_b200 import _cabi
+    from pbs_attn_b200.prefill import get_plan, permuted_block_sparse_attn_fwd
+    from pbs_attn_b200.sharding import gather_heads, shard_heads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.load()
+    peaks = load_peaks()
+
+    sh = shard_heads(w.q_heads, w.kv_heads, rank, world)
+    wl = w.with_(q_heads=sh.q_count, kv_heads=sh.kv_count)
+    q, k, v = make_qkv(wl, args.seed + rank, device=dev)
+    torch.cuda.synchronize()
+
+    def step():
+        out = permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, True)
+        if world > 1:
+            out = gather_heads(out, w.q_heads, w.kv_heads)
+        return out
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    plan = get_plan(q, sh.kv_count, w.block_size, w.segment_size)
+    plan.check_status()
+    n_sel_local = float(plan.block_mask.sum().item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.pbs_launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    barrier()
+    ev[0].record()
+    for _ in range(args.steps):
+        out = step()
+    ev[1].record()
+    barrier()
+    launches = lib.pbs_launch_count() - launches0
+    ms_total = ev[0].elapsed_time(ev[1])
+    plan.check_status()
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(out.shape if world == 1 else (w.batch, sh.q_count, w.seq_len, w.head_dim), dtype=q.dtype).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        o = permuted_block_sparse_attn_fwd(dq, dk, dv, w.block_size, w.segment_size, w.threshold, True)
+        ho.copy_(o, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 3))
+    ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev2[0].record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev2[1].record()
+    barrier()
+    e2e_ms_total = ev2[0].elapsed_time(ev2[1])
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-stage device times on this rank (the attention kernel gives the roofline)
+    opt = plan.options(w.threshold)
+    o2 = torch.empty_like(q)
+    stage_calls = [
+        ("key_importance", lambda: plan.key_importance(q, k)),
+        ("segment_permute", lambda: plan.segment_permute(k, v)),
+        ("pool_queries", lambda: plan.pool_queries(q)),
+        ("select_blocks", lambda: plan.select_blocks(opt)),
+        ("tile_lists", lambda: plan.build_tile_lists()),
+        ("attention", lambda: plan.attn_fwd(q, o2)),
+    ]
+    reps = max(1, min(args.steps, 3))
+    stage_ms = {}
+    for name, fn in stage_calls:
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        stage_ms[name] = a.elapsed_time(b) / reps
+    plan.check_status()
+
+    # ---- reduce over ranks: time = max, work = sum
+    t = torch.tensor([ms_total, e2e_ms_total, stage_ms["attention"]], dtype=torch.float64, device=dev)
+    work = torch.tensor([n_sel_local], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms_total, attn_ms_max = (float(x) for x in t.tolist())
+    n_sel = float(work.item())
+
+    if rank == 0:
+        ms_step = ms_total / args.steps
+        fl_sel = selected_flops(n_sel, w)
+        fl_dense = dense_equiv_flops(w, w.q_heads)
+        nb = -(-w.seq_len // w.block_size)
+        causal_blocks = w.batch * w.q_heads * nb * (nb + 1) / 2
+        value = fl_sel / (ms_step * 1e-3) / 1e12
+        e2e_ms = e2e_ms_total / e2e_steps
+        e2e_val = fl_sel / (e2e_ms * 1e-3) / 1e12
+        esz = q.element_size()
+        h2d = (q.numel() + k.numel() + v.numel()) * esz
+        d2h = ho.numel() * esz
+        # attention kernel of THIS rank: its own selected blocks over its own duration
+        attn_s = stage_ms["attention"] * 1e-3
+        achieved = selected_flops(n_sel_local, w) / attn_s / 1e12
+        long_step = stage_ms["attention"] > 50.0
+        peak = peaks["bf16_sustained"] if long_step else peaks["bf16_burst"]
+        B, Hq, Hkv, S, D, bs = w.batch, sh.q_count, sh.kv_count, w.seq_len, w.head_dim, w.block_size
+        L = (S // w.segment_size) * w.segment_size
+        stage_bytes = {      # algorithmic HBM bytes per launch group (this rank's heads)
+            "key_importance": B * Hkv * L * D * esz + B * Hq * bs * D * esz + 2 * B * Hq * bs * L * esz + 4 * B * Hq * L,
+            "segment_permute": 2 * B * Hkv * S * D * esz + 4 * B * Hq * L + 2 * B * Hq * S * D * esz + 4 * B * Hq * S + B * Hq * nb * D * esz,
+            "pool_queries": B * Hq * S * D * esz + B * Hq * nb * D * esz,
+            "select_blocks": 2 * B * Hq * nb * D * esz + B * Hq * nb * nb,
+            "tile_lists": B * Hq * nb * nb + 4 * B * Hq * ((S + 255) // 256) * ((S + 127) // 128),
+        }
+        stages = {n: {"ms": round(ms, 4)} for n, ms in stage_ms.items()}
+        for n, by in stage_bytes.items():
+            stages[n]["gbs"] = round(by / (stage_ms[n] * 1e-3) / 1e9, 1)
+            stages[n]["frac_hbm"] = round(stages[n]["gbs"] / peaks["hbm_gbs"], 4)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": config_dict(w, world),
+            "density": n_sel / causal_blocks,
+            "selected_tflop_per_step": fl_sel / 1e12, "dense_equiv_tflop_per_step": fl_dense / 1e12,
+            "dense_equiv_tflops": fl_dense / (ms_step * 1e-3) / 1e12,
+            "frac_bf16_peak": value / world / peak,
+            "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
+                    "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "attn_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": f"{peaks['source']} ({'sustained' if long_step else 'burst'})",
+                         "kernel_ms": stage_ms["attention"], "kernel_ms_max_over_ranks": attn_ms_max},
+            "stages": stages,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
+            ws = sample_workload(w)
+            dt, fl = cpu_port_run(ws, args.seed)
+            line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
+                                    "kind": "port", "seconds": dt, "sample": sample_text(ws)}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama8b_heads_s131072", choices=sorted(WORKLOADS))
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--threshold", type=float, default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.seq_len:
+        w = w.with_(seq_len=args.seq_len, name=f"{w.name.rsplit('_s', 1)[0]}_s{args.seq_len}")
+    if args.threshold is not None:
+        w = w.with_(threshold=args.threshold)
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

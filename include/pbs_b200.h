@@ -100,6 +100,8 @@ typedef struct {
 
 const char* pbs_last_error_string(void);
 int pbs_version(void);
+/* Number of kernels this library has launched in the calling process so far. */
+int64_t pbs_launch_count(void);
 
 /* Validates the shape and fills the scratch element counts. */
 int pbs_scratch_sizes(const pbs_shape_t* shape, pbs_scratch_sizes_t* sizes);
@@ -131,12 +133,14 @@ int pbs_pool_queries(const pbs_shape_t* shape, const void* q, const int64_t q_st
 
 /* Stage 2b.  Pooled logits, fp32 softmax over the kv blocks of earlier segments,
  * cumulative-threshold selection, then OR of the first-token block and of the q block's
- * own segment.  block_mask is (B, Hq, nb, nb) bytes of 0/1.
+ * own segment.  block_mask is (B, Hq, nb, nb) bytes of 0/1.  block_scores may be NULL; if given,
+ * (B, Hq, nb, nb) floats receive the pooled softmax scores the reference's
+ * permuted_block_selection also returns (0 outside the candidates; for inspection and tests).
  * Replaces pbs_attn/src/utils.py:30-34 (block_pooled_attn), :38-86 (select_blocks),
  * pbs_attn/src/pbs.py:95-127 (permuted_block_selection) and :209. */
 int pbs_select_blocks(const pbs_shape_t* shape, const void* pooled_q, const void* pooled_k,
                       const int32_t* first_block, const pbs_options_t* options,
-                      uint8_t* block_mask, void* stream);
+                      uint8_t* block_mask, float* block_scores, void* stream);
 
 /* Stage 3a.  Per 256-query group, the compact list of 128-key tiles that any of its
  * query blocks selected (consumed by the tcgen05 attention kernel). */

@@ -49,12 +49,12 @@ SIGNATURES = {
     "pbs_key_importance": [_SH, _P, _ST, _P, _ST, _P, _P, _P, _P, _P],
     "pbs_segment_permute": [_SH, _P, _P, _ST, _P, _ST, _P, _P, _P, _P, C.c_int32, _P, _P],
     "pbs_pool_queries": [_SH, _P, _ST, _P, C.c_int32, _P],
-    "pbs_select_blocks": [_SH, _P, _P, _P, C.POINTER(Options), _P, _P],
+    "pbs_select_blocks": [_SH, _P, _P, _P, C.POINTER(Options), _P, _P, _P],
     "pbs_build_tile_lists": [_SH, _P, _P, _P, _P],
     "pbs_attn_fwd": [_SH, _P, _ST, _P, _P, _P, _P, _P, _P, _P, _ST, C.c_int32, _P, _P],
     "pbs_prefill_fwd": [_SH, _P, _ST, _P, _ST, _P, _ST, _P, _ST, C.POINTER(Options), C.POINTER(Scratch), _P],
 }
-EXPORTS = ["pbs_last_error_string", "pbs_version"] + list(SIGNATURES)
+EXPORTS = ["pbs_last_error_string", "pbs_version", "pbs_launch_count"] + list(SIGNATURES)
 
 _lib = None
 
@@ -77,6 +77,8 @@ def load():
     lib.pbs_last_error_string.argtypes = []
     lib.pbs_version.restype = C.c_int
     lib.pbs_version.argtypes = []
+    lib.pbs_launch_count.restype = C.c_int64
+    lib.pbs_launch_count.argtypes = []
     for name, args in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = C.c_int

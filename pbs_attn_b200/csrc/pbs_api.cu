@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 
 #include "pbs_common.cuh"
 
@@ -15,6 +16,9 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int cuda_fail(cudaError_t e, const char* what) {
   set_error("%s: %s", what, cudaGetErrorString(e));
@@ -75,6 +79,7 @@ extern "C" {
 
 const char* pbs_last_error_string(void) { return g_err; }
 int pbs_version(void) { return 100; }
+int64_t pbs_launch_count(void) { return (int64_t)g_launches.load(); }
 
 int pbs_scratch_sizes(const pbs_shape_t* shape, pbs_scratch_sizes_t* z) {
   PBS_TRY(check_shape(shape));
@@ -137,11 +142,11 @@ int pbs_pool_queries(const pbs_shape_t* shape, const void* q, const int64_t q_st
 
 int pbs_select_blocks(const pbs_shape_t* shape, const void* pooled_q, const void* pooled_k,
                       const int32_t* first_block, const pbs_options_t* options, uint8_t* block_mask,
-                      void* stream) {
+                      float* block_scores, void* stream) {
   PBS_TRY(check_shape(shape));
   PBS_NONNULL(pooled_q); PBS_NONNULL(pooled_k); PBS_NONNULL(first_block); PBS_NONNULL(options); PBS_NONNULL(block_mask);
   return launch_select_blocks(make_dims(*shape), shape->dtype, pooled_q, pooled_k, first_block, *options, block_mask,
-                              (cudaStream_t)stream);
+                              block_scores, (cudaStream_t)stream);
 }
 
 int pbs_build_tile_lists(const pbs_shape_t* shape, const uint8_t* block_mask, uint32_t* tile_list,
@@ -207,7 +212,7 @@ int pbs_prefill_fwd(const pbs_shape_t* shape, const void* q, const int64_t q_str
     PBS_TRY(pbs_segment_permute(shape, sc->importance, k, k_strides, v, v_strides, sc->key_indices, sc->perm_k,
                                 sc->perm_v, sc->pooled_k, options->key_pool_mode, sc->first_block, stream));
     PBS_TRY(pbs_pool_queries(shape, q, q_strides, sc->pooled_q, options->query_pool_mode, stream));
-    PBS_TRY(pbs_select_blocks(shape, sc->pooled_q, sc->pooled_k, sc->first_block, options, sc->block_mask, stream));
+    PBS_TRY(pbs_select_blocks(shape, sc->pooled_q, sc->pooled_k, sc->first_block, options, sc->block_mask, nullptr, stream));
   }
   const Dims d = make_dims(attn_shape);
   int impl = options->attn_impl;

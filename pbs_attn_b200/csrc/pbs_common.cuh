@@ -119,10 +119,13 @@ static inline int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p;
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 
+void count_launch();
+
 #define PBS_CUDA_CHECK_LAUNCH(what)                                   \
   do {                                                                \
     cudaError_t e__ = cudaGetLastError();                             \
     if (e__ != cudaSuccess) return ::pbs::cuda_fail(e__, what);       \
+    ::pbs::count_launch();                                            \
   } while (0)
 
 // Stage launchers (defined one per .cu file).
@@ -134,7 +137,8 @@ int launch_segment_permute(const Dims& d, int dt, const float* importance, const
 int launch_pool_queries(const Dims& d, int dt, const void* q, Strides qs, void* pooled_q, int pool_mode,
                         cudaStream_t st);
 int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void* pooled_k,
-                         const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, cudaStream_t st);
+                         const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, float* scores,
+                         cudaStream_t st);
 int launch_fill_mask_ones(const Dims& d, uint8_t* mask, cudaStream_t st);
 int launch_build_tile_lists(const Dims& d, const uint8_t* mask, uint32_t* list, int32_t* count, cudaStream_t st);
 int launch_attn_simt(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,

@@ -22,7 +22,7 @@ template <int DT>
 __global__ void __launch_bounds__(SEL_THREADS)
 select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename Elem<DT>::T* __restrict__ pooled_k,
               const int32_t* __restrict__ first_block, const float* __restrict__ thr_per_head, float thr_scalar,
-              int select_all, int force_first, uint8_t* __restrict__ mask,
+              int select_all, int force_first, uint8_t* __restrict__ mask, float* __restrict__ scores,
               int Hq, int D, int nb, int bps, float sqrt_d, int npow2_max) {
   using E = Elem<DT>;
   using T = typename E::T;
@@ -39,10 +39,14 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
   const int h = bh % Hq;
   const int ncand = (qb / bps) * bps;                  // kv blocks of earlier segments
   uint8_t* row = mask + ((int64_t)bh * nb + qb) * nb;
+  float* srow = scores ? scores + ((int64_t)bh * nb + qb) * nb : nullptr;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float thr = thr_per_head ? thr_per_head[h] : thr_scalar;
 
-  for (int i = threadIdx.x; i < nb; i += blockDim.x) row[i] = 0;
+  for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+    row[i] = 0;
+    if (srow) srow[i] = 0.f;
+  }
   if (threadIdx.x == 0) first_rank = 0x7fffffff;
   __syncthreads();
 
@@ -91,6 +95,7 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
       if (i < ncand) {
         float p = vals[i] / z;
         if (p != p) p = 0.f;                           // nan_to_num
+        if (srow) srow[i] = p;
         key = ((unsigned long long)float_order_key(p) << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)i);
       }
       keys[i] = key;
@@ -202,7 +207,8 @@ tile_list_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ list, 
 }  // namespace
 
 int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void* pooled_k,
-                         const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, cudaStream_t st) {
+                         const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, float* scores,
+                         cudaStream_t st) {
   const int npow2 = next_pow2(d.nb);
   const size_t smem = (size_t)npow2 * 8 + (size_t)d.D * 4 + (size_t)d.nb * 4;
   dim3 grid(d.nb, d.B * d.Hq);
@@ -216,7 +222,7 @@ int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void
     }                                                                                                         \
     kern<<<grid, SEL_THREADS, smem, st>>>((const TT*)pooled_q, (const TT*)pooled_k, first_block,              \
                                           opt.threshold_per_head, opt.threshold, opt.select_all,             \
-                                          opt.force_select_first_block, mask, d.Hq, d.D, d.nb, d.bps, sq,    \
+                                          opt.force_select_first_block, mask, scores, d.Hq, d.D, d.nb, d.bps, sq,    \
                                           npow2);                                                             \
   }
   switch (dt) {

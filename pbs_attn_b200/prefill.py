@@ -130,10 +130,15 @@ class Plan:
         _cabi.check(self.lib.pbs_pool_queries(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.pooled_q),
                                               _cabi.POOL[query_pool_mode], self._stream()), "pbs_pool_queries")
 
-    def select_blocks(self, opt: _cabi.Options):
+    def select_blocks(self, opt: _cabi.Options, want_scores: bool = False):
+        """Returns the (B, Hq, nb, nb) fp32 pooled scores when ``want_scores`` (else None)."""
+        scores = None
+        if want_scores:
+            scores = torch.empty(self.block_mask.shape, dtype=torch.float32, device=self.device)
         _cabi.check(self.lib.pbs_select_blocks(C.byref(self.shape), _ptr(self.pooled_q), _ptr(self.pooled_k),
                                                _ptr(self.first_block), C.byref(opt), _ptr(self.block_mask),
-                                               self._stream()), "pbs_select_blocks")
+                                               _ptr(scores), self._stream()), "pbs_select_blocks")
+        return scores
 
     def build_tile_lists(self):
         _cabi.check(self.lib.pbs_build_tile_lists(C.byref(self.shape), _ptr(self.block_mask), _ptr(self.tile_list),

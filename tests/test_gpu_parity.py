@@ -32,30 +32,57 @@ def _oracle(w, kwargs, q, k, v):
     return pbs_oracle.permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, **kwargs)
 
 
+REL_ULP = {"bf16": 2.0 ** -7, "fp16": 2.0 ** -10}
+
+
+def _check_logits(mine, ref, dtype, what):
+    """Scoring logits (fp32 accumulate, rounded to the input dtype at the reference's two rounding
+    points).  The summation order of a GEMM is not part of the reference's contract, so a bf16/fp16
+    logit may land on the neighbouring representable value; that must stay rare and never be more
+    than one step.  Returns the fraction of differing logits."""
+    a, b = mine.float(), ref.float()
+    if dtype == "fp32":
+        assert torch.allclose(a, b, rtol=2e-5, atol=1e-6), f"{what}: fp32 logits differ"
+        return 0.0
+    diff = a != b
+    frac = diff.float().mean().item()
+    assert frac < 2e-3, f"{what}: {frac:.2e} of the logits differ"
+    step = REL_ULP[dtype] * torch.maximum(a.abs(), b.abs()) * 1.0001
+    assert bool(((a - b).abs() <= step)[diff].all()), f"{what}: a logit differs by more than one rounding step"
+    return frac
+
+
 @pytest.mark.parametrize("name", SPARSE_CASES)
 def test_stage_importance_and_permutation(name):
-    """Stage 1: importance close to the oracle's; given the ORACLE's importance the sort, gather and
-    key pooling are bit-exact; given our own importance the permutation differs only at near-ties."""
+    """Stage 1.  (a) our scoring logits equal the reference's up to rare one-step rounding flips;
+    (b) from OUR logits, the reference's softmax/mean/argsort (run on CPU) gives exactly our
+    permutation, except fp32 near-ties (relative 2e-5); (c) given the ORACLE's importance, sort,
+    gather, key pooling and first-token block are bit-exact."""
+    import math
     w, kwargs, stride, (q, k, v), g = load_case(name)
     r = _oracle(w, kwargs, q, k, v)
     qd, kd, vd = _dev(q, k, v)
     plan = _plan(w, qd)
+    n_rep = w.q_heads // w.kv_heads
+    L = plan.n_complete
     imp = plan.key_importance(qd, kd).cpu()
-    rel = ((imp - r.importance).abs() / r.importance.abs().clamp_min(1e-30)).max().item()
-    assert rel < 2e-4, f"importance max relative error {rel:.2e}"
+    mine = plan.logits[: w.batch * w.q_heads * w.block_size * L].view(w.batch, w.q_heads, w.block_size, L).cpu()
+    ref = torch.matmul(q[:, :, -w.block_size:], pbs_oracle.repeat_kv(k, n_rep)[:, :, :L].transpose(-1, -2)) / math.sqrt(w.head_dim)
+    _check_logits(mine, ref, w.dtype, name)
+    imp_from_mine = torch.softmax(mine.float(), dim=-1).mean(dim=-2)
+    rel = ((imp - imp_from_mine).abs() / imp_from_mine.abs().clamp_min(1e-30)).max().item()
+    assert rel < 2e-5, f"importance vs fp32 softmax of our own logits: max relative error {rel:.2e}"
 
     kmode = kwargs.get("key_pool_mode", "mean")
     plan.segment_permute(kd, vd, kmode)
-    n_diff, n_bad = classify_permutation(plan.key_indices.cpu(), r.key_indices, r.importance, w.segment_size)
-    assert n_bad == 0, f"{n_bad} of {n_diff} differing permutation slots are not near-ties"
-    gold_diff, gold_bad = classify_permutation(plan.key_indices.cpu(), torch.from_numpy(g["idx_stable"]), r.importance, w.segment_size)
-    assert gold_bad == 0
+    expect = pbs_oracle.segment_permutation(imp_from_mine, w.seq_len, w.segment_size, stable=True)
+    n_diff, n_bad = classify_permutation(plan.key_indices.cpu(), expect, imp_from_mine, w.segment_size)
+    assert n_bad == 0, f"{n_bad} of {n_diff} differing permutation slots are not fp32 near-ties"
 
     # exactness of sort + gather + pooling, isolated from the importance arithmetic
     plan.importance[: r.importance.numel()].copy_(r.importance.reshape(-1).cuda())
     plan.segment_permute(kd, vd, kmode)
     assert torch.equal(plan.key_indices.cpu().long(), r.key_indices)
-    n_rep = w.q_heads // w.kv_heads
     pk = pbs_oracle.gather_rows(pbs_oracle.repeat_kv(k, n_rep), r.key_indices)
     pv = pbs_oracle.gather_rows(pbs_oracle.repeat_kv(v, n_rep), r.key_indices)
     assert torch.equal(plan.perm_k.cpu(), pk) and torch.equal(plan.perm_v.cpu(), pv)
@@ -67,8 +94,10 @@ def test_stage_importance_and_permutation(name):
 
 @pytest.mark.parametrize("name", SPARSE_CASES)
 def test_stage_selection(name):
-    """Stage 2 on the ORACLE's permuted keys: pooled Q bit-exact; mask equal to the oracle's except
-    rows explained by score ties or a running sum within 2e-6 of the threshold."""
+    """Stage 2 on the ORACLE's permuted keys.  Pooled Q is bit-exact; our pooled scores equal the
+    oracle's up to rare one-step logit flips; the reference's select_blocks run on OUR scores gives
+    our mask, except rows whose running sum is within 2e-6 of the threshold or that cut through
+    equal scores; with the oracle's own scores the same classification holds."""
     w, kwargs, stride, (q, k, v), g = load_case(name)
     r = _oracle(w, kwargs, q, k, v)
     qd, kd, vd = _dev(q, k, v)
@@ -79,12 +108,25 @@ def test_stage_selection(name):
     plan.pool_queries(qd, qmode)
     pq = pbs_oracle._pool(pbs_oracle._pad_to_block(q, w.block_size), w.block_size, qmode)
     assert torch.equal(plan.pooled_q.cpu(), pq)
-    opt = plan.options(w.threshold, kwargs.get("force_select_first_block", True), qmode, kmode)
-    plan.select_blocks(opt)
+    force = kwargs.get("force_select_first_block", True)
+    opt = plan.options(w.threshold, force, qmode, kmode)
+    scores = plan.select_blocks(opt, want_scores=True).cpu()
     mask = plan.block_mask.cpu().bool()
-    rows, bad = classify_mask(mask, r.block_mask, r.block_scores, float(w.threshold), w.segment_size // w.block_size)
+    ref_scores = torch.nan_to_num(r.block_scores, nan=0.0)
+    off = (scores - ref_scores).abs() > 1e-5 * ref_scores.abs() + 1e-12
+    assert off.float().mean().item() < 2e-3, "pooled scores differ from the oracle's beyond rare rounding flips"
+    bps = w.segment_size // w.block_size
+    if not (isinstance(w.threshold, int) and w.threshold == 1):
+        nb = mask.shape[-1]
+        _, same = pbs_oracle.candidate_block_mask(nb, bps)
+        expect = pbs_oracle.select_blocks(scores, w.threshold, stable=True)
+        if force:
+            expect = expect | pbs_oracle.first_token_blocks(r.key_indices, w.seq_len, w.block_size)
+        expect = expect | same[None, None]
+        rows, bad = classify_mask(mask, expect, scores, float(w.threshold), bps)
+        assert bad == 0, f"{bad} of {rows} rows differ from select_blocks run on our own scores"
+    rows, bad = classify_mask(mask, r.block_mask, r.block_scores, float(w.threshold), bps)
     assert bad == 0, f"{bad} of {rows} differing mask rows are unexplained"
-    # fp32 inputs have no quantisation ties: demand exact equality there
     if w.dtype == "fp32":
         assert torch.equal(mask, r.block_mask)
 
@@ -134,17 +176,27 @@ def test_whole_path_against_reference_fixtures(name):
         return
     r = _oracle(w, kwargs, q, k, v)
     nb = -(-w.seq_len // w.block_size)
+    bps = w.segment_size // w.block_size
     idx = inter["key_indices"].cpu()
-    n_diff, n_bad = classify_permutation(idx, torch.from_numpy(g["idx_stable"]), r.importance, w.segment_size)
+    # permutation vs the reference fixture: exact for fp32; for bf16/fp16 a one-step flip of a scoring
+    # logit may swap keys whose importance is within 2 % of each other, and only a handful of slots
+    rel = 2e-5 if w.dtype == "fp32" else 2e-2
+    n_diff, n_bad = classify_permutation(idx, torch.from_numpy(g["idx_stable"]), r.importance, w.segment_size, rel=rel)
     assert n_bad == 0, f"{n_bad}/{n_diff} permutation slots unexplained"
-    if n_diff == 0:
-        # same permutation => the masks are comparable row by row
-        mask = inter["block_mask"].cpu().bool()
-        rows, bad = classify_mask(mask, golden_mask(g, "stable", nb), r.block_scores, float(w.threshold),
-                                  w.segment_size // w.block_size)
-        assert bad == 0, f"{bad}/{rows} mask rows unexplained"
-        if w.dtype == "fp32":
-            assert np.array_equal(idx.numpy(), g["idx_stable"]) and rows == 0
+    assert n_diff <= max(4, int(1e-3 * idx.numel())), f"{n_diff} permutation slots differ"
+    if w.dtype == "fp32":
+        assert np.array_equal(idx.numpy(), g["idx_stable"])
+    # mask: the reference's selection run (on CPU) on OUR permutation must give our mask
+    n_rep = w.q_heads // w.kv_heads
+    pk = pbs_oracle.gather_rows(pbs_oracle.repeat_kv(k, n_rep), idx.long())
+    expect, scores = pbs_oracle.block_selection(q, pk, idx.long(), w.block_size, w.segment_size, w.threshold,
+                                                kwargs.get("force_select_first_block", True),
+                                                kwargs.get("query_pool_mode", "mean"), kwargs.get("key_pool_mode", "mean"))
+    mask = inter["block_mask"].cpu().bool()
+    rows, bad = classify_mask(mask, expect, scores, float(w.threshold), bps)
+    assert bad == 0, f"{bad}/{rows} mask rows unexplained"
+    if n_diff == 0 and w.dtype == "fp32":
+        assert torch.equal(mask, golden_mask(g, "stable", nb))
 
 
 def test_repeated_kv_equals_grouped_kv():
