@@ -37,9 +37,10 @@ REL_ULP = {"bf16": 2.0 ** -7, "fp16": 2.0 ** -10}
 
 def _check_logits(mine, ref, dtype, what):
     """Scoring logits (fp32 accumulate, rounded to the input dtype at the reference's two rounding
-    points).  The summation order of a GEMM is not part of the reference's contract, so a bf16/fp16
-    logit may land on the neighbouring representable value; that must stay rare and never be more
-    than one step.  Returns the fraction of differing logits."""
+    points).  The summation order of a GEMM is not part of the reference's contract, so the first
+    rounding of a bf16/fp16 logit may land on the neighbouring representable value, which the
+    division by sqrt(D) and the second rounding can turn into at most two steps of the result; that
+    must stay rare.  Returns the fraction of differing logits."""
     a, b = mine.float(), ref.float()
     if dtype == "fp32":
         assert torch.allclose(a, b, rtol=2e-5, atol=1e-6), f"{what}: fp32 logits differ"
@@ -47,8 +48,8 @@ def _check_logits(mine, ref, dtype, what):
     diff = a != b
     frac = diff.float().mean().item()
     assert frac < 2e-3, f"{what}: {frac:.2e} of the logits differ"
-    step = REL_ULP[dtype] * torch.maximum(a.abs(), b.abs()) * 1.0001
-    assert bool(((a - b).abs() <= step)[diff].all()), f"{what}: a logit differs by more than one rounding step"
+    step = 2.0 * REL_ULP[dtype] * torch.maximum(a.abs(), b.abs()) * 1.0001
+    assert bool(((a - b).abs() <= step)[diff].all()), f"{what}: a logit differs by more than two rounding steps"
     return frac
 
 
@@ -113,10 +114,11 @@ def test_stage_selection(name):
     scores = plan.select_blocks(opt, want_scores=True).cpu()
     mask = plan.block_mask.cpu().bool()
     ref_scores = torch.nan_to_num(r.block_scores, nan=0.0)
-    off = (scores - ref_scores).abs() > 1e-5 * ref_scores.abs() + 1e-12
-    assert off.float().mean().item() < 2e-3, "pooled scores differ from the oracle's beyond rare rounding flips"
     bps = w.segment_size // w.block_size
-    if not (isinstance(w.threshold, int) and w.threshold == 1):
+    select_all = isinstance(w.threshold, int) and w.threshold == 1      # scores are not needed then
+    if not select_all:
+        off = (scores - ref_scores).abs() > 1e-5 * ref_scores.abs() + 1e-12
+        assert off.float().mean().item() < 2e-3, "pooled scores differ from the oracle's beyond rare rounding flips"
         nb = mask.shape[-1]
         _, same = pbs_oracle.candidate_block_mask(nb, bps)
         expect = pbs_oracle.select_blocks(scores, w.threshold, stable=True)
@@ -170,8 +172,14 @@ def test_whole_path_against_reference_fixtures(name):
     inter["plan"].check_status()
     assert out.shape == q.shape and out.dtype == q.dtype and out.stride() == qd.stride()
     sub = out.cpu()[:, :, ::stride, :]
-    assert_close_out(sub, golden_out(g, "stable", w.torch_dtype), w.torch_dtype, name + " vs stable-sort reference")
-    assert_close_out(sub, golden_out(g, "ref", w.torch_dtype), w.torch_dtype, name + " vs unmodified reference")
+    want_stable, want_ref = golden_out(g, "stable", w.torch_dtype), golden_out(g, "ref", w.torch_dtype)
+    assert_close_out(sub, want_stable, w.torch_dtype, name + " vs stable-sort reference")
+    # The unmodified reference breaks score ties in an implementation-defined order; where its own
+    # two runs differ (same code, stable vs non-stable sort) that spread is added to the max bound.
+    spread = (want_ref.float() - want_stable.float()).abs().max().item()
+    d = (sub.float() - want_ref.float()).abs()
+    assert d.mean().item() <= TOL[w.torch_dtype][1], f"{name} vs unmodified reference: mean-abs {d.mean().item():.3e}"
+    assert d.max().item() <= TOL[w.torch_dtype][0] + spread, f"{name} vs unmodified reference: max-abs {d.max().item():.3e}"
     if "idx_stable" not in g:
         return
     r = _oracle(w, kwargs, q, k, v)
