@@ -131,6 +131,17 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 template <int DT> struct PackP;
 template <> struct PackP<PBS_BF16> {
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
@@ -152,7 +163,7 @@ struct Bars {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[NK], k_empty[NK];
   uint64_t v_full[NV], v_empty[NV];
-  uint64_t s_full[2], p_full[2], o_full[2];
+  uint64_t s_full[2], p_full[2][2], o_full[2];   // p_full[tile][half]
 };
 
 struct Params {
@@ -223,7 +234,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(smem_u32(&bars->q_full[i]), 1);
       mbar_init(smem_u32(&bars->q_empty[i]), 1);
       mbar_init(smem_u32(&bars->s_full[i]), 1);
-      mbar_init(smem_u32(&bars->p_full[i]), 128);
+      mbar_init(smem_u32(&bars->p_full[i][0]), 128);
+      mbar_init(smem_u32(&bars->p_full[i][1]), 128);
       mbar_init(smem_u32(&bars->o_full[i]), 1);
     }
     for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 1); }
@@ -249,6 +261,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   constexpr uint32_t kFmt = (DT == PBS_BF16) ? 1u : 0u;
   constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
   constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | (((uint32_t)D >> 3) << 17) | ((128u >> 4) << 24);
+
 
   if (warp == 0) {
     // =========================================================================== TMA producer
@@ -312,12 +325,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         tc_commit(smem_u32(&bars->s_full[i]));
       };
-      auto issue_pv = [&](int i, uint32_t vstage, bool accumulate) {
+      // half = 0 / 1: keys 0-63 / 64-127 of the tile, 16 per instruction
+      auto issue_pv_half = [&](int i, uint32_t vstage, bool accumulate, int half) {
         const uint32_t b0 = sbase + SM::kV + vstage * kTile;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)                    // 128 keys, 16 per instruction
+        for (int ks = 4 * half; ks < 4 * half + 4; ++ks)
           mma_ts(tmem_O[i], tmem_S[i] + ks * 8, smem_desc(b0 + ks * 2048, kSlab, 1024), kIdescPV, (accumulate || ks > 0));
-        tc_commit(smem_u32(&bars->o_full[i]));
+        if (half == 1) tc_commit(smem_u32(&bars->o_full[i]));
       };
 
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
@@ -351,11 +365,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           bool k_ready = false;
           for (int i = 0; i < 2 && ok; ++i) {
             if (cur & (1u << (16 + i))) {
-              ok = wait_bar(smem_u32(&bars->p_full[i]), pc[i] & 1u, ctl, p.status, 7);
+              for (int half = 0; half < 2 && ok; ++half) {
+                ok = wait_bar(smem_u32(&bars->p_full[i][half]), pc[i] & 1u, ctl, p.status, 7);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv_half(i, vs, started[i], half);
+              }
               if (!ok) break;
               ++pc[i];
-              tc_fence_after();
-              issue_pv(i, vs, started[i]);
               started[i] = true;
             }
             if (nxt & (1u << (16 + i))) {
@@ -386,7 +403,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int row = wq * 32 + lane;
     const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
     int32_t* kidx = reinterpret_cast<int32_t*>(smem + SM::kIdx) + (warp - 4) * 128;
-    const uint32_t bar_s = smem_u32(&bars->s_full[i]), bar_p = smem_u32(&bars->p_full[i]), bar_o = smem_u32(&bars->o_full[i]);
+    const uint32_t bar_s = smem_u32(&bars->s_full[i]), bar_o = smem_u32(&bars->o_full[i]);
+    const uint32_t bar_p[2] = {smem_u32(&bars->p_full[i][0]), smem_u32(&bars->p_full[i][1])};
     uint32_t sc = 0;                                       // softmax steps done = PVs requested so far
     bool ok = true;
 
@@ -422,52 +440,49 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
 
-        uint32_t sr[4][32];
+        // Masks of this tile for the 64 columns starting at col0 (compile-time), applied in both
+        // passes: keys of the own segment that lie after the query, and 64x64 sub-blocks that were
+        // not selected (block_size 64 only).
+        const bool drop_half[2] = {p.bs == 64 && !((bits >> (2 * (row >> 6) + 0)) & 1u),
+                                   p.bs == 64 && !((bits >> (2 * (row >> 6) + 1)) & 1u)};
+        auto mask64 = [&](float (&v)[64], int half) {
+          if (elem_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + c * 32, sr[c]);
-        tmem_wait_ld();
-        float* s = reinterpret_cast<float*>(&sr[0][0]);
-
-        if (elem_mask) {
+            for (int c = 0; c < 64; ++c)
+              if (kidx[64 * half + c] > qpos) v[c] = -CUDART_INF_F;
+          }
+          if (drop_half[half]) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c)
-            if (kidx[c] > qpos) s[c] = -CUDART_INF_F;
+            for (int c = 0; c < 64; ++c) v[c] = -CUDART_INF_F;
+          }
+        };
+        // pass 1: row maximum (3-input max, two chains per half), S read 64 columns at a time
+        float mx[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sr[2][32];
+          tmem_ld32(tmem_S[i] + lane_off + 64 * half, sr[0]);
+          tmem_ld32(tmem_S[i] + lane_off + 64 * half + 32, sr[1]);
+          tmem_wait_ld();
+          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[0][0]);
+          mask64(v, half);
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
+#pragma unroll
+            for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
+            mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
+          }
         }
-        if (p.bs == 64) {                                  // 64x64 sub-blocks that were not selected
-          const int qi = row >> 6;
-#pragma unroll
-          for (int ki = 0; ki < 2; ++ki)
-            if (!((bits >> (2 * qi + ki)) & 1u)) {
-#pragma unroll
-              for (int c = 0; c < 64; ++c) s[ki * 64 + c] = -CUDART_INF_F;
-            }
-        }
-        float mt = s[0];
-#pragma unroll
-        for (int c = 1; c < 128; ++c) mt = fmaxf(mt, s[c]);
-        mt *= p.scale_log2e;
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
 
         float alpha = 1.f;
         if (mt > m_used + kRescaleThreshold) {             // also the first finite maximum
-          alpha = exp2f(m_used - mt);                      // 0 when m_used is -inf
+          alpha = ex2(m_used - mt);                        // 0 when m_used is -inf
           m_used = mt;
           l *= alpha;
         }
         const bool rescale = steps > 0 && __any_sync(0xffffffffu, alpha != 1.f);
-        const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-        float lsum = 0.f;
-        uint32_t pk[2][32];
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float p0 = exp2f(fmaf(s[2 * c], p.scale_log2e, -m_eff));
-          const float p1 = exp2f(fmaf(s[2 * c + 1], p.scale_log2e, -m_eff));
-          lsum += p0 + p1;
-          pk[c >> 5][c & 31] = PackP<DT>::pack(p0, p1);
-        }
-        l += lsum;
-        tmem_st32(tmem_S[i] + lane_off, pk[0]);
-        tmem_st32(tmem_S[i] + lane_off + 32, pk[1]);
-
         if (rescale) {
           // O_i holds the sum up to the previous step: wait for that PV, then scale in place
           ok = __all_sync(0xffffffffu, wait_bar(bar_o, (sc - 1u) & 1u, ctl, p.status, 10));
@@ -483,9 +498,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tmem_st32(tmem_O[i] + lane_off + c * 32, o);
           }
         }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_p);
+        const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+        const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
+        const float2 nm2 = make_float2(-m_eff, -m_eff);
+        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        // P goes back in two halves of 64 keys: the MMA issuer starts O += P V on the first half
+        // while the second half is still being exponentiated
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sr[2][32];
+          tmem_ld32(tmem_S[i] + lane_off + 64 * half, sr[0]);
+          tmem_ld32(tmem_S[i] + lane_off + 64 * half + 32, sr[1]);
+          tmem_wait_ld();
+          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[0][0]);
+          mask64(v, half);
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float2 x = __ffma2_rn(make_float2(v[2 * c], v[2 * c + 1]), sc2, nm2);
+            const float2 e = make_float2(ex2(x.x), ex2(x.y));
+            acc2[c & 1] = __fadd2_rn(acc2[c & 1], e);
+            pk[c] = PackP<DT>::pack(e.x, e.y);
+          }
+          tmem_st32(tmem_S[i] + lane_off + 32 * half, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_p[half]);
+        }
+        l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
         ++sc;
         ++steps;
       }

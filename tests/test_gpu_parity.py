@@ -48,7 +48,9 @@ def _check_logits(mine, ref, dtype, what):
     diff = a != b
     frac = diff.float().mean().item()
     assert frac < 2e-3, f"{what}: {frac:.2e} of the logits differ"
-    step = 2.0 * REL_ULP[dtype] * torch.maximum(a.abs(), b.abs()) * 1.0001
+    # plus an absolute slack for logits near zero, where the fp32 dot product itself (terms of
+    # magnitude ~1 that cancel) is only accurate to ~1e-5
+    step = 2.0 * REL_ULP[dtype] * torch.maximum(a.abs(), b.abs()) * 1.0001 + 2e-5
     assert bool(((a - b).abs() <= step)[diff].all()), f"{what}: a logit differs by more than two rounding steps"
     return frac
 
