@@ -8,7 +8,8 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libpbs_b200.so")
+# PBS_B200_LIB points at an alternative build of the same library (e.g. an instrumented one)
+_LIB_PATH = os.environ.get("PBS_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libpbs_b200.so")
 
 BF16, FP16, FP32 = 0, 1, 2
 POOL = {"mean": 0, "max": 1}

@@ -10,14 +10,14 @@
 // tiles that either query tile selected.  A persistent CTA (one per SM) walks its items with
 // twelve warps in four roles:
 //   warp 0      TMA producer: Q tiles, then K and V tiles of the list into two 2-deep rings
-//   warp 1      MMA issuer:   S_i = Q_i K^T (SS, both operands K-major, 128B swizzle) and
-//                             O_i += P_i V  (TS: P read from TMEM, V MN-major from shared memory)
+//   warps 1, 3  MMA issuers, one per query tile: S_i = Q_i K^T (SS, both operands K-major, 128B
+//               swizzle) and O_i += P_i V (TS: P read from TMEM, V MN-major from shared memory)
 //   warp 2      owns the TMEM allocation (all 512 columns: S0 S1 O0 O1, 128 columns each)
 //   warps 4-7   softmax of query tile 0: tcgen05.ld S, mask, row max / exp2 / row sum, P written
 //   warps 8-11  softmax of query tile 1  back over the first 64 columns of S as packed 16-bit
 //                             pairs; lazy rescale of O in TMEM; final O / l epilogue to global
-// The MMA issue order interleaves the two query tiles (PV0, QK0', PV1, QK1') so one tile's softmax
-// overlaps the other tile's MMAs.  Every wait on an mbarrier is bounded; when one runs out the CTA
+// Each issuer runs PV_i(e), QK_i(e+1) per list entry, so one tile's softmax overlaps the other
+// tile's MMAs and one issuer's barrier bookkeeping overlaps the other issuer's MMAs.  Every wait on an mbarrier is bounded; when one runs out the CTA
 // raises a flag, all roles leave their loops, TMEM is freed and status[0] tells the host.
 #include <cuda.h>
 
@@ -57,6 +57,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One lane of a fully converged warp; the surrounding code stays warp-uniform, which lets the
+// compiler keep descriptors and addresses in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, %1;\n\t"
+      "@px mov.s32 %0, 1;\n\t}"
+      : "+r"(pred)
+      : "r"(0xFFFFFFFFu));
+  return pred != 0;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -78,19 +90,33 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Executed by a converged warp; one elected lane commits.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
+  if (elect_one())
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem], accumulate flag known at compile time (no predicate set-up).
+template <bool ACC>
+__device__ __forceinline__ void mma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  if (elect_one())
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  if (elect_one())
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
       : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (elect_one())
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
@@ -156,6 +182,23 @@ template <> struct PackP<PBS_FP16> {
   }
 };
 
+// Optional timeline trace (compiled in with -DPBS_TC_TRACE only): CTA 0 records clock64() stamps of
+// its MMA issuer and of lane 0 of each softmax warpgroup's first warp.
+#ifdef PBS_TC_TRACE
+__device__ long long g_trace[4][4096];
+__device__ int g_trace_n[4];
+#define PBS_TRACE_DECL int trace_n__ = 0
+#define PBS_TRACE(role, tag)                                                                     \
+  do {                                                                                           \
+    if (blockIdx.x == 0 && trace_n__ < 4096) g_trace[role][trace_n__++] = (clock64() << 4) | (tag); \
+  } while (0)
+#define PBS_TRACE_END(role) do { if (blockIdx.x == 0) g_trace_n[role] = trace_n__; } while (0)
+#else
+#define PBS_TRACE_DECL do { } while (0)
+#define PBS_TRACE(role, tag) do { } while (0)
+#define PBS_TRACE_END(role) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan
 // ---------------------------------------------------------------------------------------------
@@ -200,6 +243,11 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctl* ctl
   }
 }
 
+// The same for a whole converged warp: every lane polls, the verdict is made warp-uniform.
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
+  return __all_sync(0xffffffffu, wait_bar(bar, parity, ctl, status, code));
+}
+
 template <int D>
 struct Smem {
   static constexpr int kTileBytes = 128 * D * 2;          // one 128-row tile
@@ -238,8 +286,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       mbar_init(smem_u32(&bars->p_full[i][1]), 128);
       mbar_init(smem_u32(&bars->o_full[i]), 1);
     }
-    for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 1); }
-    for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 1); }
+    for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 2); }
+    for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 2); }
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -265,7 +313,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   if (warp == 0) {
     // =========================================================================== TMA producer
-    if (lane == 0) {
+    // The whole warp walks the lists (uniform control flow); one elected lane issues the copies.
+    {
       uint32_t kc = 0, vc = 0, qc[2] = {0, 0};
       bool ok = true;
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
@@ -274,127 +323,160 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int i = 0; i < 2 && ok; ++i) {
           const int r0 = g * 256 + i * 128;
           if (r0 >= p.S) continue;
-          ok = wait_bar(smem_u32(&bars->q_empty[i]), (qc[i] & 1u) ^ 1u, ctl, p.status, 1);
+          ok = wait_bar_warp(smem_u32(&bars->q_empty[i]), (qc[i] & 1u) ^ 1u, ctl, p.status, 1);
           if (!ok) break;
           const uint32_t bar = smem_u32(&bars->q_full[i]);
-          mbar_expect_tx(bar, kTile);
-          for (int kh = 0; kh < KH; ++kh)
-            tma_load_4d(sbase + SM::kQ + i * kTile + kh * kSlab, &map_q, bar, kh * 64, r0, h, b);
+          if (elect_one()) {
+            mbar_expect_tx(bar, kTile);
+            for (int kh = 0; kh < KH; ++kh)
+              tma_load_4d(sbase + SM::kQ + i * kTile + kh * kSlab, &map_q, bar, kh * 64, r0, h, b);
+          }
           ++qc[i];
         }
         const int n = p.count[(int64_t)bh * p.G + g];
         const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
+        uint32_t ent = n > 0 ? lst[0] : 0u;
         for (int e = 0; e < n && ok; ++e) {
-          const int t = (int)(lst[e] & 0xFFFFu);
+          const int t = (int)(ent & 0xFFFFu);
+          if (e + 1 < n) ent = lst[e + 1];                 // fetched one entry ahead of its use
           {
             const uint32_t s = kc % NK;
-            ok = wait_bar(smem_u32(&bars->k_empty[s]), ((kc / NK) & 1u) ^ 1u, ctl, p.status, 2);
+            ok = wait_bar_warp(smem_u32(&bars->k_empty[s]), ((kc / NK) & 1u) ^ 1u, ctl, p.status, 2);
             if (!ok) break;
             const uint32_t bar = smem_u32(&bars->k_full[s]);
-            mbar_expect_tx(bar, kTile);
-            for (int kh = 0; kh < KH; ++kh)
-              tma_load_3d(sbase + SM::kK + s * kTile + kh * kSlab, &map_k, bar, kh * 64, t * 128, bh);
+            if (elect_one()) {
+              mbar_expect_tx(bar, kTile);
+              for (int kh = 0; kh < KH; ++kh)
+                tma_load_3d(sbase + SM::kK + s * kTile + kh * kSlab, &map_k, bar, kh * 64, t * 128, bh);
+            }
             ++kc;
           }
           {
             const uint32_t s = vc % NV;
-            ok = wait_bar(smem_u32(&bars->v_empty[s]), ((vc / NV) & 1u) ^ 1u, ctl, p.status, 3);
+            ok = wait_bar_warp(smem_u32(&bars->v_empty[s]), ((vc / NV) & 1u) ^ 1u, ctl, p.status, 3);
             if (!ok) break;
             const uint32_t bar = smem_u32(&bars->v_full[s]);
-            mbar_expect_tx(bar, kTile);
-            for (int kh = 0; kh < KH; ++kh)
-              tma_load_3d(sbase + SM::kV + s * kTile + kh * kSlab, &map_v, bar, kh * 64, t * 128, bh);
+            if (elect_one()) {
+              mbar_expect_tx(bar, kTile);
+              for (int kh = 0; kh < KH; ++kh)
+                tma_load_3d(sbase + SM::kV + s * kTile + kh * kSlab, &map_v, bar, kh * 64, t * 128, bh);
+            }
             ++vc;
           }
         }
       }
       if (!ok) __nanosleep(200000);                       // let copies in flight land before teardown
     }
-  } else if (warp == 1) {
-    // =========================================================================== MMA issuer
-    if (lane == 0) {
-      uint32_t kc = 0, vc = 0, qc[2] = {0, 0}, pc[2] = {0, 0};
+  } else if (warp == 1 || warp == 3) {
+    // =========================================================================== MMA issuers
+    // Warp 1 issues for query tile 0, warp 3 for query tile 1.  Control flow is uniform for the
+    // whole warp; each tcgen05.mma / commit is issued by one elected lane.  Both warps walk the
+    // whole list (the K/V ring is indexed by list position) and act on the entries their tile uses;
+    // a ring stage is free again once BOTH have committed on its `empty` barrier.  The bookkeeping
+    // of one warp (barrier waits, list reads) overlaps the other warp's MMAs on the tensor pipe.
+    {
+      const int i = warp >> 1;                              // query tile of this issuer
+      uint32_t kc = 0, vc = 0, qc = 0, pc = 0;
       bool ok = true;
+      PBS_TRACE_DECL;
+      const uint32_t use_bit = 1u << (16 + i);
 
-      auto issue_qk = [&](int i, uint32_t kstage) {
-        const uint32_t a0 = sbase + SM::kQ + i * kTile, b0 = sbase + SM::kK + kstage * kTile;
+      // Descriptors are built once; per instruction only a compile-time constant is added to the
+      // start-address field.
+      const uint64_t dq = smem_desc(sbase + SM::kQ + i * kTile, 16, 1024);
+      const uint32_t bar_sfull = smem_u32(&bars->s_full[i]), bar_ofull = smem_u32(&bars->o_full[i]);
+      const uint32_t tS = tmem_S[i], tO = tmem_O[i];
+
+      auto issue_qk = [&](uint32_t kstage) {
+        const uint64_t b0 = smem_desc(sbase + SM::kK + kstage * kTile, 16, 1024);
+        mma_ss_c<false>(tS, dq, b0, kIdescQK);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kSlab + (ks & 3) * 32;
-          mma_ss(tmem_S[i], smem_desc(a0 + off, 16, 1024), smem_desc(b0 + off, 16, 1024), kIdescQK, ks > 0);
+        for (int ks = 1; ks < D / 16; ++ks) {
+          const uint64_t off = (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
+          mma_ss_c<true>(tS, dq + off, b0 + off, kIdescQK);
         }
-        tc_commit(smem_u32(&bars->s_full[i]));
+        tc_commit(bar_sfull);
       };
       // half = 0 / 1: keys 0-63 / 64-127 of the tile, 16 per instruction
-      auto issue_pv_half = [&](int i, uint32_t vstage, bool accumulate, int half) {
-        const uint32_t b0 = sbase + SM::kV + vstage * kTile;
+      auto issue_pv_half = [&](uint32_t vstage, bool accumulate, int half) {
+        const uint64_t b0 = smem_desc(sbase + SM::kV + vstage * kTile, kSlab, 1024) + (uint64_t)half * ((4 * 2048) >> 4);
+        const uint32_t a0 = tS + half * 32;
+        if (half == 0) mma_ts(tO, a0, b0, kIdescPV, accumulate);
+        else mma_ts_c<true>(tO, a0, b0, kIdescPV);
 #pragma unroll
-        for (int ks = 4 * half; ks < 4 * half + 4; ++ks)
-          mma_ts(tmem_O[i], tmem_S[i] + ks * 8, smem_desc(b0 + ks * 2048, kSlab, 1024), kIdescPV, (accumulate || ks > 0));
-        if (half == 1) tc_commit(smem_u32(&bars->o_full[i]));
+        for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tO, a0 + ks * 8, b0 + (uint64_t)((ks * 2048) >> 4), kIdescPV);
+        if (half == 1) tc_commit(bar_ofull);
       };
 
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
         const int bh = item / p.G, g = p.G - 1 - item % p.G;
         const int n = p.count[(int64_t)bh * p.G + g];
         const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
-        bool have[2];
-        for (int i = 0; i < 2; ++i) {
-          have[i] = g * 256 + i * 128 < p.S;
-          if (have[i] && ok) { ok = wait_bar(smem_u32(&bars->q_full[i]), qc[i] & 1u, ctl, p.status, 4); ++qc[i]; }
-        }
-        if (!ok) break;
-        bool started[2] = {false, false};                 // O_i holds a partial sum of this item
-        uint32_t cur = n > 0 ? lst[0] : 0u;
-        if (n > 0) {
-          const uint32_t s = kc % NK;
-          ok = wait_bar(smem_u32(&bars->k_full[s]), (kc / NK) & 1u, ctl, p.status, 5);
+        const bool have = g * 256 + i * 128 < p.S;
+        if (have) {
+          ok = wait_bar_warp(smem_u32(&bars->q_full[i]), qc & 1u, ctl, p.status, 4);
+          ++qc;
           if (!ok) break;
-          tc_fence_after();
-          for (int i = 0; i < 2; ++i)
-            if (cur & (1u << (16 + i))) issue_qk(i, s);
+        }
+        bool started = false;                               // O_i holds a partial sum of this item
+        uint32_t cur = n > 0 ? lst[0] : 0u;
+        uint32_t nxt = n > 1 ? lst[1] : 0u;
+        if (n > 0) {
+          // A stage's `full` barrier is awaited even when this tile skips the entry: an issuer must
+          // not arrive on `empty` for a later round of the stage before the other issuer has arrived
+          // for this one.
+          const uint32_t s = kc % NK;
+          ok = wait_bar_warp(smem_u32(&bars->k_full[s]), (kc / NK) & 1u, ctl, p.status, 5);
+          if (!ok) break;
+          if (cur & use_bit) {
+            tc_fence_after();
+            issue_qk(s);
+          }
           tc_commit(smem_u32(&bars->k_empty[s]));
           ++kc;
         }
         for (int e = 0; e < n && ok; ++e) {
-          const uint32_t nxt = (e + 1 < n) ? lst[e + 1] : 0u;
+          const uint32_t nn = (e + 2 < n) ? lst[e + 2] : 0u;    // read two entries ahead of its use
           const uint32_t vs = vc % NV;
-          ok = wait_bar(smem_u32(&bars->v_full[vs]), (vc / NV) & 1u, ctl, p.status, 6);
+          if (lane == 0) PBS_TRACE(i, 6);
+          ok = wait_bar_warp(smem_u32(&bars->v_full[vs]), (vc / NV) & 1u, ctl, p.status, 6);
           if (!ok) break;
-          const uint32_t ks = kc % NK;
-          bool k_ready = false;
-          for (int i = 0; i < 2 && ok; ++i) {
-            if (cur & (1u << (16 + i))) {
-              for (int half = 0; half < 2 && ok; ++half) {
-                ok = wait_bar(smem_u32(&bars->p_full[i][half]), pc[i] & 1u, ctl, p.status, 7);
-                if (!ok) break;
-                tc_fence_after();
-                issue_pv_half(i, vs, started[i], half);
-              }
+          if (cur & use_bit) {
+            for (int half = 0; half < 2 && ok; ++half) {
+              if (lane == 0) PBS_TRACE(i, 0);
+              ok = wait_bar_warp(smem_u32(&bars->p_full[i][half]), pc & 1u, ctl, p.status, 7);
               if (!ok) break;
-              ++pc[i];
-              started[i] = true;
+              if (lane == 0) PBS_TRACE(i, 1);
+              tc_fence_after();
+              issue_pv_half(vs, started, half);
             }
-            if (nxt & (1u << (16 + i))) {
-              if (!k_ready) {
-                ok = wait_bar(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
-                if (!ok) break;
-                tc_fence_after();
-                k_ready = true;
-              }
-              issue_qk(i, ks);
-            }
+            if (!ok) break;
+            ++pc;
+            started = true;
           }
-          if (!ok) break;
           tc_commit(smem_u32(&bars->v_empty[vs]));
           ++vc;
-          if (nxt) { tc_commit(smem_u32(&bars->k_empty[ks])); ++kc; }
+          if (nxt) {
+            const uint32_t ks = kc % NK;
+            if (lane == 0) PBS_TRACE(i, 8);
+            ok = wait_bar_warp(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
+            if (!ok) break;
+            if (lane == 0) PBS_TRACE(i, 9);
+            if (nxt & use_bit) {
+              tc_fence_after();
+              issue_qk(ks);
+              if (lane == 0) PBS_TRACE(i, 4);
+            }
+            tc_commit(smem_u32(&bars->k_empty[ks]));
+            ++kc;
+          }
           cur = nxt;
+          nxt = nn;
         }
         if (!ok) break;
-        for (int i = 0; i < 2; ++i)
-          if (have[i]) tc_commit(smem_u32(&bars->q_empty[i]));
+        if (have) tc_commit(smem_u32(&bars->q_empty[i]));
       }
+      if (lane == 0) PBS_TRACE_END(i);
     }
   } else if (warp >= 4) {
     // =========================================================================== softmax + epilogue
@@ -407,6 +489,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t bar_p[2] = {smem_u32(&bars->p_full[i][0]), smem_u32(&bars->p_full[i][1])};
     uint32_t sc = 0;                                       // softmax steps done = PVs requested so far
     bool ok = true;
+    PBS_TRACE_DECL;
 
     for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
       const int bh = item / p.G, g = p.G - 1 - item % p.G;
@@ -436,9 +519,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           __syncwarp();
         }
+        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 0);
         ok = __all_sync(0xffffffffu, wait_bar(bar_s, sc & 1u, ctl, p.status, 9));
         if (!ok) break;
         tc_fence_after();
+        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 1);
 
         // Masks of this tile for the 64 columns starting at col0 (compile-time), applied in both
         // passes: keys of the own segment that lie after the query, and 64x64 sub-blocks that were
@@ -456,25 +541,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int c = 0; c < 64; ++c) v[c] = -CUDART_INF_F;
           }
         };
-        // pass 1: row maximum (3-input max, two chains per half), S read 64 columns at a time
+        // pass 1: row maximum (3-input max, four chains); all 128 columns are loaded at once
         float mx[4];
+        {
+          uint32_t sr[4][32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t sr[2][32];
-          tmem_ld32(tmem_S[i] + lane_off + 64 * half, sr[0]);
-          tmem_ld32(tmem_S[i] + lane_off + 64 * half + 32, sr[1]);
+          for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + 32 * c, sr[c]);
           tmem_wait_ld();
-          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[0][0]);
-          mask64(v, half);
 #pragma unroll
-          for (int a = 0; a < 2; ++a) {
-            float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
+          for (int half = 0; half < 2; ++half) {
+            float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[2 * half][0]);
+            mask64(v, half);
 #pragma unroll
-            for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
-            mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
+            for (int a = 0; a < 2; ++a) {
+              float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
+#pragma unroll
+              for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
+              mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
+            }
           }
         }
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
+        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 2);
 
         float alpha = 1.f;
         if (mt > m_used + kRescaleThreshold) {             // also the first finite maximum
@@ -524,6 +612,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(bar_p[half]);
+          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3 + half);
         }
         l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
         ++sc;
@@ -564,6 +653,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // the next item's first P V overwrites O_i: order our TMEM reads before the arrive that lets it go
       tc_fence_before();
     }
+    if (wq == 0 && lane == 0) PBS_TRACE_END(2 + i);
   }
 
   // =============================================================================== teardown
@@ -656,6 +746,16 @@ int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void*
 }
 
 }  // namespace
+
+#ifdef PBS_TC_TRACE
+extern "C" int pbs_debug_read_trace(long long* host_buf, int* counts) {
+  cudaMemcpyFromSymbol(host_buf, g_trace, sizeof(long long) * 4 * 4096);
+  cudaMemcpyFromSymbol(counts, g_trace_n, sizeof(int) * 4);
+  int zero[4] = {0, 0, 0, 0};
+  cudaMemcpyToSymbol(g_trace_n, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 bool attn_tc_supported(const Dims& d, int dt) {
   return (dt == PBS_BF16 || dt == PBS_FP16) && (d.D == 64 || d.D == 128) && (d.bs == 64 || d.bs == 128) &&
