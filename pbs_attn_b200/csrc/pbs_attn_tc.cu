@@ -504,8 +504,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       float l = 0.f;
       uint32_t steps = 0;                                  // softmax steps of this item
 
+      uint32_t ent_next = n > 0 ? lst[0] : 0u;
       for (int e = 0; e < n && ok; ++e) {
-        const uint32_t ent = lst[e];
+        const uint32_t ent = ent_next;
+        if (e + 1 < n) ent_next = lst[e + 1];              // fetched one entry ahead of its use
         if (!(ent & (1u << (16 + i)))) continue;
         const int t = (int)(ent & 0xFFFFu);
         const bool elem_mask = ent & (1u << (18 + i));
