@@ -115,6 +115,22 @@ int pbs_key_importance(const pbs_shape_t* shape,
                        void* logits, void* partials, void* rowstats,
                        float* importance, void* stream);
 
+/* Stage 1a without caller scratch.  No counterpart in the reference: it exists for hosts that can
+ * pass only inputs and outputs and may not allocate device memory themselves (a plugin boundary
+ * that owns all memory, a running serving loop where cudaMalloc could stall the device).  Same
+ * result as pbs_key_importance; the logits and softmax statistics live in an array built into the
+ * library (PBS_STATIC_SCRATCH_BYTES on every GPU that loads it, until the process exits).  Shapes
+ * whose scratch exceeds that size are rejected with PBS_ERR_SHAPE.  Never calls cudaMalloc/cudaFree.
+ * The first call on a device looks up the array's address (cudaGetSymbolAddress, that device must be
+ * current); make that first call before starting any stream capture.  All calls on a device share
+ * the one array, which keeps the previous call's contents (the stage overwrites all it reads, so
+ * nothing needs clearing): two calls that overlap on the GPU race -- serialise them on one stream. */
+#define PBS_STATIC_SCRATCH_BYTES (64u << 20)
+int pbs_key_importance_static(const pbs_shape_t* shape,
+                              const void* q, const int64_t q_strides[4],
+                              const void* k, const int64_t k_strides[4],
+                              float* importance, void* stream);
+
 /* Stage 1b.  Stable descending sort of the importance inside each segment, gather of
  * K and V rows into permuted order, block pooling of the permuted K, and the index of
  * the permuted block that holds original token 0.

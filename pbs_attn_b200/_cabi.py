@@ -14,6 +14,7 @@ _LIB_PATH = os.environ.get("PBS_B200_LIB") or os.path.join(os.path.dirname(os.pa
 BF16, FP16, FP32 = 0, 1, 2
 POOL = {"mean": 0, "max": 1}
 ATTN_IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
+STATIC_SCRATCH_BYTES = 64 << 20
 
 
 class Shape(C.Structure):
@@ -48,6 +49,7 @@ _ST = C.POINTER(C.c_int64)
 SIGNATURES = {
     "pbs_scratch_sizes": [_SH, C.POINTER(ScratchSizes)],
     "pbs_key_importance": [_SH, _P, _ST, _P, _ST, _P, _P, _P, _P, _P],
+    "pbs_key_importance_static": [_SH, _P, _ST, _P, _ST, _P, _P],
     "pbs_segment_permute": [_SH, _P, _P, _ST, _P, _ST, _P, _P, _P, _P, C.c_int32, _P, _P],
     "pbs_pool_queries": [_SH, _P, _ST, _P, C.c_int32, _P],
     "pbs_select_blocks": [_SH, _P, _P, _P, C.POINTER(Options), _P, _P, _P],

@@ -159,6 +159,22 @@ class Plan:
         return out
 
 
+def key_importance_static(q: torch.Tensor, k: torch.Tensor, block_size: int, segment_size: int) -> torch.Tensor:
+    """Key importance (B, Hq, L) through ``pbs_key_importance_static``: only q, k and the result are
+    passed, the stage's scratch is the array built into the library (see include/pbs_b200.h for who
+    needs this and its 64 MiB limit).  The result tensor is the caller's; the call allocates nothing
+    on the C side."""
+    lib = _cabi.load()
+    B, Hq, S, D = q.shape
+    shape = _cabi.Shape(B, Hq, k.shape[1], S, D, block_size, segment_size, _DTYPES[q.dtype])
+    L = (S // segment_size) * segment_size
+    out = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
+    stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+    _cabi.check(lib.pbs_key_importance_static(C.byref(shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                              _ptr(out), stream), "pbs_key_importance_static")
+    return out
+
+
 _PLANS: dict = {}
 _MAX_PLANS = 2
 
