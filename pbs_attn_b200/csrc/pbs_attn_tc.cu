@@ -136,15 +136,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -543,24 +549,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int c = 0; c < 64; ++c) v[c] = -CUDART_INF_F;
           }
         };
-        // pass 1: row maximum (3-input max, four chains); all 128 columns are loaded at once
+        // S is read from TMEM once (a load round trip costs several hundred cycles) and stays in
+        // registers for both the maximum and the exponentiation.
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + 32 * c, sr[c]);
+        tmem_wait_ld();
         float mx[4];
-        {
-          uint32_t sr[4][32];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + 32 * c, sr[c]);
-          tmem_wait_ld();
+        for (int half = 0; half < 2; ++half) {
+          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[2 * half][0]);
+          mask64(v, half);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[2 * half][0]);
-            mask64(v, half);
+          for (int a = 0; a < 2; ++a) {
+            float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
 #pragma unroll
-            for (int a = 0; a < 2; ++a) {
-              float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
-#pragma unroll
-              for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
-              mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
-            }
+            for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
+            mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
           }
         }
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
@@ -579,43 +584,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tmem_O[i] + lane_off + c * 32, o);
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st32(tmem_O[i] + lane_off + c * 32, o);
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st16(tmem_O[i] + lane_off + c * 16, o);
           }
         }
         const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
         const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
         const float2 nm2 = make_float2(-m_eff, -m_eff);
         float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        // P goes back in two halves of 64 keys: the MMA issuer starts O += P V on the first half
-        // while the second half is still being exponentiated
+        // P goes back in four stores of 32 keys (16 TMEM columns each) and is handed to the MMA
+        // issuer in two halves of 64 keys, so O += P V starts on the first half while the second is
+        // still being exponentiated.  The first half's stores are awaited only after the third
+        // quarter has been computed, which hides their round trip.
+        const float* sv = reinterpret_cast<const float*>(&sr[0][0]);
+        uint32_t pk[16];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t sr[2][32];
-          tmem_ld32(tmem_S[i] + lane_off + 64 * half, sr[0]);
-          tmem_ld32(tmem_S[i] + lane_off + 64 * half + 32, sr[1]);
-          tmem_wait_ld();
-          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[0][0]);
-          mask64(v, half);
-          uint32_t pk[32];
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float2 x = __ffma2_rn(make_float2(v[2 * c], v[2 * c + 1]), sc2, nm2);
-            const float2 e = make_float2(ex2(x.x), ex2(x.y));
-            acc2[c & 1] = __fadd2_rn(acc2[c & 1], e);
-            pk[c] = PackP<DT>::pack(e.x, e.y);
+          for (int c = 0; c < 16; ++c) {
+            const int col = 32 * q + 2 * c;
+            const float2 x = __ffma2_rn(make_float2(sv[col], sv[col + 1]), sc2, nm2);
+            const float2 ex = make_float2(ex2(x.x), ex2(x.y));
+            acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
+            pk[c] = PackP<DT>::pack(ex.x, ex.y);
           }
-          tmem_st32(tmem_S[i] + lane_off + 32 * half, pk);
-          tmem_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar_p[half]);
-          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3 + half);
+          if (q == 2) {
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar_p[0]);
+            if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3);
+          }
+          tmem_st16(tmem_S[i] + lane_off + 16 * q, pk);
         }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p[1]);
+        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 4);
         l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
         ++sc;
         ++steps;
@@ -631,24 +640,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const float inv = l > 0.f ? 1.f / l : 0.f;
       T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)qpos * p.os.s;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
+      for (int c = 0; c < D / 16; ++c) {
+        uint32_t o[16];
         if (steps > 0) {
-          tmem_ld32(tmem_O[i] + lane_off + c * 32, o);
+          tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0u;
+          for (int j = 0; j < 16; ++j) o[j] = 0u;
         }
         if (qpos < p.S) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < 2; ++j) {
             uint4 w;
             w.x = PackP<DT>::pack(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
             w.y = PackP<DT>::pack(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
             w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
             w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + j * 8) = w;
+            *reinterpret_cast<uint4*>(orow + c * 16 + j * 8) = w;
           }
         }
       }
