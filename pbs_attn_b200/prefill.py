@@ -248,3 +248,97 @@ def permuted_block_sparse_attn_fwd(
     if os.environ.get("PBS_B200_CHECK_STATUS") == "1":
         plan.check_status()
     return out
+
+
+class _HostPipeline:
+    """Streams and device staging buffers of ``permuted_block_sparse_attn_fwd_host`` for one shape."""
+
+    def __init__(self, B, hq_c, hkv_c, S, D, dtype, device):
+        self.copy_in = torch.cuda.Stream(device)
+        self.copy_out = torch.cuda.Stream(device)
+        mk = lambda h: [torch.empty(B, h, S, D, dtype=dtype, device=device) for _ in range(2)]
+        self.q, self.k, self.v, self.o = mk(hq_c), mk(hkv_c), mk(hkv_c), mk(hq_c)
+
+
+_HOST_PIPES: dict = {}
+
+
+def permuted_block_sparse_attn_fwd_host(
+    query_states: torch.Tensor,
+    key_states: torch.Tensor,
+    value_states: torch.Tensor,
+    block_size: int,
+    segment_size: int,
+    threshold,
+    causal: bool = True,
+    force_select_first_block: bool = True,
+    query_pool_mode: str = "mean",
+    key_pool_mode: str = "mean",
+    out: Optional[torch.Tensor] = None,
+    device=None,
+    chunks: Optional[int] = None,
+) -> torch.Tensor:
+    """The same call for HOST tensors (ideally pinned): q (B, Hq, S, D), k/v (B, Hkv, S, D) in CPU
+    memory, result in CPU memory.
+
+    Query heads are independent, so the call is cut into ``chunks`` groups of whole KV heads and
+    pipelined over three streams: while group g is computed, group g+1 is copied in and group g-1 is
+    copied out (PCIe is full duplex), with two device staging buffers per operand.  Only the first
+    group's upload and the last group's download are exposed.  Returns after enqueueing everything;
+    synchronise (``torch.cuda.synchronize``) before reading ``out``.
+    """
+    assert causal and not query_states.is_cuda
+    B, Hq, S, D = query_states.shape
+    Hkv = key_states.shape[1]
+    assert Hq % Hkv == 0 and key_states.shape == value_states.shape and key_states.shape[2] == S
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    if chunks is None:
+        chunks = Hkv
+    if Hkv % chunks:
+        raise ValueError(f"chunks={chunks} does not divide the {Hkv} KV heads")
+    hkv_c, hq_c = Hkv // chunks, Hq // chunks
+    if out is None:
+        out = torch.empty(B, Hq, S, D, dtype=query_states.dtype).pin_memory()
+    key = (B, hq_c, hkv_c, S, D, query_states.dtype, dev.index)
+    pipe = _HOST_PIPES.get(key)
+    if pipe is None:
+        _HOST_PIPES.clear()
+        pipe = _HOST_PIPES[key] = _HostPipeline(B, hq_c, hkv_c, S, D, query_states.dtype, dev)
+    plan = get_plan(pipe.q[0], hkv_c, block_size, segment_size)
+    opt = plan.options(threshold, force_select_first_block, query_pool_mode, key_pool_mode)
+    main = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(main)
+    pipe.copy_in.wait_event(start)
+    pipe.copy_out.wait_event(start)
+    done_compute = [None, None]      # last compute that read staging slot s
+    done_out = [None, None]          # last download that read output slot s
+    for c in range(chunks):
+        s = c & 1
+        qs, ks = slice(c * hq_c, (c + 1) * hq_c), slice(c * hkv_c, (c + 1) * hkv_c)
+        with torch.cuda.stream(pipe.copy_in):
+            if done_compute[s] is not None:
+                pipe.copy_in.wait_event(done_compute[s])
+            for dst, src in ((pipe.q[s], query_states[:, qs]), (pipe.k[s], key_states[:, ks]), (pipe.v[s], value_states[:, ks])):
+                for b in range(B):
+                    dst[b].copy_(src[b], non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(pipe.copy_in)
+        main.wait_event(ev_in)
+        if done_out[s] is not None:
+            main.wait_event(done_out[s])
+        plan.run(pipe.q[s], pipe.k[s], pipe.v[s], pipe.o[s], opt)
+        done_compute[s] = torch.cuda.Event()
+        done_compute[s].record(main)
+        with torch.cuda.stream(pipe.copy_out):
+            pipe.copy_out.wait_event(done_compute[s])
+            for b in range(B):
+                out[b, qs].copy_(pipe.o[s][b], non_blocking=True)
+            done_out[s] = torch.cuda.Event()
+            done_out[s].record(pipe.copy_out)
+    for ev in done_out:
+        if ev is not None:
+            main.wait_event(ev)
+    return out

@@ -255,3 +255,16 @@ def test_bad_pool_mode_raises_value_error():
     q = torch.zeros(1, 2, 512, 64, device="cuda")
     with pytest.raises(ValueError):
         permuted_block_sparse_attn_fwd(q, q, q, 64, 256, 0.9, True, query_pool_mode="median")
+
+
+def test_host_buffer_call_equals_device_call():
+    """The pipelined host-buffer entry (chunked by KV head, three streams) gives the device call's
+    result bit for bit."""
+    from pbs_attn_b200.prefill import permuted_block_sparse_attn_fwd, permuted_block_sparse_attn_fwd_host
+    w, kwargs, stride, (q, k, v), g = load_case("llama_bf16_s4096")
+    want = permuted_block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), w.block_size, w.segment_size, w.threshold, True)
+    for chunks in (None, 1):
+        got = permuted_block_sparse_attn_fwd_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), w.block_size,
+                                                  w.segment_size, w.threshold, True, chunks=chunks)
+        torch.cuda.synchronize()
+        assert not got.is_cuda and torch.equal(got, want.cpu())
