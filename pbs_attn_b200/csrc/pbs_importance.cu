@@ -109,20 +109,149 @@ logits_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
   }
 }
 
-__global__ void rowstats_kernel(const float2* __restrict__ partials, float2* __restrict__ rowstats,
-                                int ntile, int bs) {
-  const int bh = blockIdx.x;
-  const int r = threadIdx.x;
+// Tensor-core variant of logits_kernel for 16-bit inputs (mma.sync m16n8k16, fp32 accumulate: the
+// products of 16-bit values are exact and the sum is rounded like any fp32 GEMM).  One CTA = 64 keys x
+// all query rows of the last block (128 per pass); warp w owns rows 16w..16w+15 of the pass.  Q and K
+// tiles sit in shared memory with 16 bytes of padding per row so ldmatrix is conflict free.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <int DT>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (DT == PBS_BF16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256)
+logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
+                  const typename Elem<DT>::T* __restrict__ k, Strides ks,
+                  typename Elem<DT>::T* __restrict__ logits, float2* __restrict__ partials,
+                  int Hq, int group, int S, int D, int bs, int L, float sqrt_d) {
+  using E = Elem<DT>;
+  using T = typename E::T;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int ld = D + 8;                                    // padded row length in elements
+  T* Qs = reinterpret_cast<T*>(smem_raw);                  // [128][ld]
+  T* Ks = Qs + 128 * ld;                                   // [64][ld]
+
+  const int jt = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / Hq, h = bh % Hq;
+  const int ntile = gridDim.x;
+  const T* qbase = q + (int64_t)b * qs.b + (int64_t)h * qs.h + (int64_t)(S - bs) * qs.s;
+  const T* kbase = k + (int64_t)b * ks.b + (int64_t)(h / group) * ks.h + (int64_t)jt * TN * ks.s;
+  const int nkeys = min(TN, L - jt * TN);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cpr = D / 8;                                   // 16-byte chunks per row
+
+  for (int i = threadIdx.x; i < TN * cpr; i += blockDim.x) {
+    const int r = i / cpr, c = i % cpr;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < nkeys) val = *reinterpret_cast<const uint4*>(kbase + (int64_t)r * ks.s + c * 8);
+    *reinterpret_cast<uint4*>(Ks + r * ld + c * 8) = val;
+  }
+  for (int r0 = 0; r0 < bs; r0 += 128) {
+    const int nrows = min(128, bs - r0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 128 * cpr; i += blockDim.x) {
+      const int r = i / cpr, c = i % cpr;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < nrows) val = *reinterpret_cast<const uint4*>(qbase + (int64_t)(r0 + r) * qs.s + c * 8);
+      *reinterpret_cast<uint4*>(Qs + r * ld + c * 8) = val;
+    }
+    __syncthreads();
+    if (warp * 16 < nrows) {
+      float acc[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc[j][t] = 0.f;
+      const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (warp * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
+      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + ((lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+      for (int d0 = 0; d0 < D; d0 += 16) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_addr + d0 * 2);
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {                   // two 8-key tiles per ldmatrix
+          uint32_t bq[4];
+          ldmatrix_x4(bq, k_addr + (jp * 16 * ld + d0) * 2);
+          mma_16816<DT>(acc[2 * jp], a, bq[0], bq[1]);
+          mma_16816<DT>(acc[2 * jp + 1], a, bq[2], bq[3]);
+        }
+      }
+      // this thread: rows lane/4 and lane/4 + 8 of the warp's 16, keys 8j + 2(lane%4), +1
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = r0 + warp * 16 + (lane >> 2) + 8 * half;
+        float y[16];
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int key = 8 * j + 2 * (lane & 3) + t;
+            y[2 * j + t] = E::rnd(E::rnd(acc[j][2 * half + t]) / sqrt_d);
+            if (key < nkeys) m = fmaxf(m, y[2 * j + t]);
+          }
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        float z = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            if (8 * j + 2 * (lane & 3) + t < nkeys) z += expf(y[2 * j + t] - m);
+        z += __shfl_xor_sync(0xffffffffu, z, 1);
+        z += __shfl_xor_sync(0xffffffffu, z, 2);
+        if (r < bs) {
+          T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int key = 8 * j + 2 * (lane & 3) + t;
+              if (key < nkeys) dst[key] = E::cvt(y[2 * j + t]);
+            }
+          if ((lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+        }
+      }
+    }
+  }
+}
+
+// One warp per (b, h, row): lanes stride the key tiles, each merging its (max, sum) pairs online,
+// then the 32 partial pairs are merged by shuffles.
+__global__ void __launch_bounds__(256)
+rowstats_kernel(const float2* __restrict__ partials, float2* __restrict__ rowstats, int ntile, int bs) {
+  const int bh = blockIdx.y;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (r >= bs) return;
   const float2* p = partials + (int64_t)bh * ntile * bs + r;
-  float m = -CUDART_INF_F;
-  for (int t = 0; t < ntile; ++t) m = fmaxf(m, p[(int64_t)t * bs].x);
-  float z = 0.f;
-  for (int t = 0; t < ntile; ++t) {
+  float m = -CUDART_INF_F, z = 0.f;
+  for (int t = lane; t < ntile; t += 32) {
     const float2 v = p[(int64_t)t * bs];
-    z += v.y * expf(v.x - m);
+    const float mn = fmaxf(m, v.x);
+    z = z * expf(m - mn) + v.y * expf(v.x - mn);
+    m = mn;
   }
-  rowstats[(int64_t)bh * bs + r] = make_float2(m, z);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float mo = __shfl_xor_sync(0xffffffffu, m, o);
+    const float zo = __shfl_xor_sync(0xffffffffu, z, o);
+    const float mn = fmaxf(m, mo);
+    const float a = (m == -CUDART_INF_F) ? 0.f : z * expf(m - mn);
+    const float c = (mo == -CUDART_INF_F) ? 0.f : zo * expf(mo - mn);
+    z = a + c;
+    m = mn;
+  }
+  if (lane == 0) rowstats[(int64_t)bh * bs + r] = make_float2(m, z);
 }
 
 template <int DT>
@@ -138,7 +267,18 @@ importance_kernel(const typename Elem<DT>::T* __restrict__ logits, const float2*
   if (j >= L) return;
   const typename E::T* col = logits + (int64_t)bh * bs * L + j;
   CascadeSum sum;
-  for (int r = 0; r < bs; ++r) {
+  int r = 0;
+  for (; r + 8 <= bs; r += 8) {                      // eight loads in flight per thread
+    float y[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) y[u] = E::ld(col + (int64_t)(r + u) * L);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float2 st = stats[r + u];
+      sum.add(expf(y[u] - st.x) / st.y);
+    }
+  }
+  for (; r < bs; ++r) {
     const float2 st = stats[r];
     sum.add(expf(E::ld(col + (int64_t)r * L) - st.x) / st.y);
   }
@@ -151,11 +291,24 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
   using T = typename Elem<DT>::T;
   const int BH = d.B * d.Hq;
   const int ntile = (d.L + TN - 1) / TN;
-  logits_kernel<DT><<<dim3(ntile, BH), 256, 0, st>>>(
-      (const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq, d.group, d.S, d.D, d.bs, d.L,
-      (float)sqrt((double)d.D));
-  PBS_CUDA_CHECK_LAUNCH("logits_kernel");
-  rowstats_kernel<<<BH, ((d.bs + 31) / 32) * 32, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
+  const float sq = (float)sqrt((double)d.D);
+  if (DT != PBS_FP32 && d.D % 16 == 0 && qs.s % 8 == 0 && ks.s % 8 == 0) {
+    // 16-bit inputs: tensor cores
+    auto kern = logits_mma_kernel<DT>;
+    const size_t smem = (size_t)(128 + TN) * (d.D + 8) * sizeof(T);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_fail(e, "logits_mma_kernel smem attribute");
+    }
+    kern<<<dim3(ntile, BH), 256, smem, st>>>((const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq,
+                                             d.group, d.S, d.D, d.bs, d.L, sq);
+    PBS_CUDA_CHECK_LAUNCH("logits_mma_kernel");
+  } else {
+    logits_kernel<DT><<<dim3(ntile, BH), 256, 0, st>>>(
+        (const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq, d.group, d.S, d.D, d.bs, d.L, sq);
+    PBS_CUDA_CHECK_LAUNCH("logits_kernel");
+  }
+  rowstats_kernel<<<dim3((d.bs + 7) / 8, BH), 256, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
   PBS_CUDA_CHECK_LAUNCH("rowstats_kernel");
   importance_kernel<DT><<<dim3((d.L + 255) / 256, BH), 256, d.bs * sizeof(float2), st>>>(
       (const T*)logits, (const float2*)rowstats, importance, d.bs, d.L);

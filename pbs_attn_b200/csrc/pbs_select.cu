@@ -58,13 +58,27 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
     while (npow2 < ncand) npow2 <<= 1;
     for (int d = threadIdx.x; d < D; d += blockDim.x) pq[d] = E::ld(pooled_q + ((int64_t)bh * nb + qb) * D + d);
     __syncthreads();
-    // pooled logits: one warp per kv block, lanes stride the head dim
-    for (int kb = warp; kb < ncand; kb += SEL_THREADS / 32) {
-      const T* pk = pooled_k + ((int64_t)bh * nb + kb) * D;
+    // pooled logits: one thread per kv block; its pooled-K row is fetched with independent 16-byte
+    // loads (all in flight together -- the rows come from L2 and latency, not bandwidth, is the cost)
+    for (int kb = threadIdx.x; kb < ncand; kb += SEL_THREADS) {
+      const uint4* pk4 = reinterpret_cast<const uint4*>(pooled_k + ((int64_t)bh * nb + kb) * D);
+      constexpr int EPV = 16 / (int)sizeof(T);           // elements per 16-byte vector
       float acc = 0.f;
-      for (int d = lane; d < D; d += 32) acc = fmaf(pq[d], E::ld(pk + d), acc);
-      acc = warp_sum(acc);
-      if (lane == 0) vals[kb] = E::rnd(E::rnd(acc) / sqrt_d);
+      for (int c0 = 0; c0 < D / EPV; c0 += 8) {
+        uint4 buf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j < D / EPV) buf[j] = pk4[c0 + j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (c0 + j < D / EPV) {
+            const T* e = reinterpret_cast<const T*>(&buf[j]);
+#pragma unroll
+            for (int t = 0; t < EPV; ++t) acc = fmaf(pq[(c0 + j) * EPV + t], E::ld(e + t), acc);
+          }
+        }
+      }
+      vals[kb] = E::rnd(E::rnd(acc) / sqrt_d);
     }
     __syncthreads();
     // fp32 softmax over the candidates
