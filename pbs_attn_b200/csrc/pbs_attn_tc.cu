@@ -30,10 +30,6 @@ constexpr int kThreads = 384;
 constexpr int NK = 2;                     // K ring depth
 constexpr int NV = 2;                     // V ring depth
 constexpr uint32_t kTmemCols = 512;
-#ifndef PBS_POLY_EVERY
-#define PBS_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = PBS_POLY_EVERY;   // 0: all exponentials on the special-function unit
 constexpr float kRescaleThreshold = 8.f;  // log2 units: O is rescaled only when the max grows by more
 
 // ---------------------------------------------------------------------------------------------
@@ -178,26 +174,6 @@ __device__ __forceinline__ float ex2(float x) {
   return r;
 }
 
-// 2^x for a pair of values on the FMA pipe instead of the special-function unit (16 results per
-// clock per SM, which bounds the exponentiation phase).  x = n + f with n = round(x) read from the
-// low mantissa bits of x + 1.5 * 2^23; 2^f by a cubic fitted on [-0.5, 0.5] (max relative error 8e-5,
-// far below the 16-bit rounding P gets); 2^n goes into the exponent field with one integer
-// multiply-add.  x is clamped at -126.
-__device__ __forceinline__ float2 exp2_fma(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 xr = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 nf = __fadd2_rn(xr, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
-  float2 q = __ffma2_rn(f, make_float2(0.05508868f, 0.05508868f), make_float2(0.24260405f, 0.24260405f));
-  q = __ffma2_rn(q, f, make_float2(0.69327623f, 0.69327623f));
-  q = __ffma2_rn(q, f, make_float2(0.99992895f, 0.99992895f));
-  float2 r;
-  r.x = __uint_as_float(__float_as_uint(xr.x) * 0x800000u + __float_as_uint(q.x));
-  r.y = __uint_as_float(__float_as_uint(xr.y) * 0x800000u + __float_as_uint(q.y));
-  return r;
-}
-
 template <int DT> struct PackP;
 template <> struct PackP<PBS_BF16> {
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
@@ -236,7 +212,7 @@ struct Bars {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[NK], k_empty[NK];
   uint64_t v_full[NV], v_empty[NV];
-  uint64_t s_full[2], p_full[2][2], o_full[2];   // p_full[tile][half]
+  uint64_t s_full[2][2], p_full[2][2], o_full[2][2];   // [query tile][key half]
 };
 
 struct Params {
@@ -312,10 +288,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->q_full[i]), 1);
       mbar_init(smem_u32(&bars->q_empty[i]), 1);
-      mbar_init(smem_u32(&bars->s_full[i]), 1);
-      mbar_init(smem_u32(&bars->p_full[i][0]), 128);
-      mbar_init(smem_u32(&bars->p_full[i][1]), 128);
-      mbar_init(smem_u32(&bars->o_full[i]), 1);
+      for (int h = 0; h < 2; ++h) {
+        mbar_init(smem_u32(&bars->s_full[i][h]), 1);
+        mbar_init(smem_u32(&bars->p_full[i][h]), 128);
+        mbar_init(smem_u32(&bars->o_full[i][h]), 1);
+      }
     }
     for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 2); }
     for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 2); }
@@ -339,7 +316,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   constexpr uint32_t kTile = SM::kTileBytes;
   // instruction descriptors: fp32 accumulate, A/B = bf16 or fp16, M = 128
   constexpr uint32_t kFmt = (DT == PBS_BF16) ? 1u : 0u;
-  constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+  constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);   // N = 64
   constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | (((uint32_t)D >> 3) << 17) | ((128u >> 4) << 24);
 
 
@@ -416,28 +393,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       // Descriptors are built once; per instruction only a compile-time constant is added to the
       // start-address field.
       const uint64_t dq = smem_desc(sbase + SM::kQ + i * kTile, 16, 1024);
-      const uint32_t bar_sfull = smem_u32(&bars->s_full[i]), bar_ofull = smem_u32(&bars->o_full[i]);
+      const uint32_t bar_sfull[2] = {smem_u32(&bars->s_full[i][0]), smem_u32(&bars->s_full[i][1])};
+      const uint32_t bar_ofull[2] = {smem_u32(&bars->o_full[i][0]), smem_u32(&bars->o_full[i][1])};
       const uint32_t tS = tmem_S[i], tO = tmem_O[i];
 
-      auto issue_qk = [&](uint32_t kstage) {
-        const uint64_t b0 = smem_desc(sbase + SM::kK + kstage * kTile, 16, 1024);
-        mma_ss_c<false>(tS, dq, b0, kIdescQK);
+      // A 128-key tile is processed as two half-steps of 64 keys (h = 0, 1), each with its own 64
+      // columns of S, so that the softmax of one half overlaps the MMAs of the other.
+      // S_h = Q K_h^T: M = 128, N = 64; K_h = rows 64h .. 64h+63 of the staged K tile.
+      auto issue_qk = [&](uint32_t kstage, int h) {
+        const uint64_t b0 = smem_desc(sbase + SM::kK + kstage * kTile + h * 64 * 128, 16, 1024);
+        const uint32_t d = tS + 64 * h;
+        mma_ss_c<false>(d, dq, b0, kIdescQK);
 #pragma unroll
         for (int ks = 1; ks < D / 16; ++ks) {
           const uint64_t off = (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
-          mma_ss_c<true>(tS, dq + off, b0 + off, kIdescQK);
+          mma_ss_c<true>(d, dq + off, b0 + off, kIdescQK);
         }
-        tc_commit(bar_sfull);
+        tc_commit(bar_sfull[h]);
       };
-      // half = 0 / 1: keys 0-63 / 64-127 of the tile, 16 per instruction
-      auto issue_pv_half = [&](uint32_t vstage, bool accumulate, int half) {
-        const uint64_t b0 = smem_desc(sbase + SM::kV + vstage * kTile, kSlab, 1024) + (uint64_t)half * ((4 * 2048) >> 4);
-        const uint32_t a0 = tS + half * 32;
-        if (half == 0) mma_ts(tO, a0, b0, kIdescPV, accumulate);
-        else mma_ts_c<true>(tO, a0, b0, kIdescPV);
+      // O += P_h V_h: P_h (64 keys as 32 columns of 16-bit pairs) sits in the first half of S_h.
+      auto issue_pv = [&](uint32_t vstage, bool accumulate, int h) {
+        const uint64_t b0 = smem_desc(sbase + SM::kV + vstage * kTile, kSlab, 1024) + (uint64_t)h * ((4 * 2048) >> 4);
+        const uint32_t a0 = tS + 64 * h;
+        mma_ts(tO, a0, b0, kIdescPV, accumulate);
 #pragma unroll
         for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tO, a0 + ks * 8, b0 + (uint64_t)((ks * 2048) >> 4), kIdescPV);
-        if (half == 1) tc_commit(bar_ofull);
+        tc_commit(bar_ofull[h]);
       };
 
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
@@ -462,43 +443,49 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (!ok) break;
           if (cur & use_bit) {
             tc_fence_after();
-            issue_qk(s);
+            issue_qk(s, 0);
+            issue_qk(s, 1);
           }
           tc_commit(smem_u32(&bars->k_empty[s]));
           ++kc;
         }
         for (int e = 0; e < n && ok; ++e) {
           const uint32_t nn = (e + 2 < n) ? lst[e + 2] : 0u;    // read two entries ahead of its use
-          const uint32_t vs = vc % NV;
+          const uint32_t vs = vc % NV, ks = kc % NK;
           if (lane == 0) PBS_TRACE(i, 6);
           ok = wait_bar_warp(smem_u32(&bars->v_full[vs]), (vc / NV) & 1u, ctl, p.status, 6);
           if (!ok) break;
-          if (cur & use_bit) {
-            for (int half = 0; half < 2 && ok; ++half) {
+          if (nxt) {
+            if (lane == 0) PBS_TRACE(i, 8);
+            ok = wait_bar_warp(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
+            if (!ok) break;
+          }
+          // per half: O += P_h V_h of this entry, then S_h of the next entry into the columns that
+          // P_h just vacated
+#pragma unroll
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (cur & use_bit) {
               if (lane == 0) PBS_TRACE(i, 0);
-              ok = wait_bar_warp(smem_u32(&bars->p_full[i][half]), pc & 1u, ctl, p.status, 7);
+              ok = wait_bar_warp(smem_u32(&bars->p_full[i][h]), pc & 1u, ctl, p.status, 7);
               if (!ok) break;
               if (lane == 0) PBS_TRACE(i, 1);
               tc_fence_after();
-              issue_pv_half(vs, started, half);
+              issue_pv(vs, started || h == 1, h);
             }
-            if (!ok) break;
+            if (nxt & use_bit) {
+              tc_fence_after();
+              issue_qk(ks, h);
+              if (lane == 0) PBS_TRACE(i, 4);
+            }
+          }
+          if (!ok) break;
+          if (cur & use_bit) {
             ++pc;
             started = true;
           }
           tc_commit(smem_u32(&bars->v_empty[vs]));
           ++vc;
           if (nxt) {
-            const uint32_t ks = kc % NK;
-            if (lane == 0) PBS_TRACE(i, 8);
-            ok = wait_bar_warp(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
-            if (!ok) break;
-            if (lane == 0) PBS_TRACE(i, 9);
-            if (nxt & use_bit) {
-              tc_fence_after();
-              issue_qk(ks);
-              if (lane == 0) PBS_TRACE(i, 4);
-            }
             tc_commit(smem_u32(&bars->k_empty[ks]));
             ++kc;
           }
@@ -517,9 +504,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int row = wq * 32 + lane;
     const uint32_t lane_off = (uint32_t)(wq * 32) << 16;
     int32_t* kidx = reinterpret_cast<int32_t*>(smem + SM::kIdx) + (warp - 4) * 128;
-    const uint32_t bar_s = smem_u32(&bars->s_full[i]), bar_o = smem_u32(&bars->o_full[i]);
+    const uint32_t bar_s[2] = {smem_u32(&bars->s_full[i][0]), smem_u32(&bars->s_full[i][1])};
     const uint32_t bar_p[2] = {smem_u32(&bars->p_full[i][0]), smem_u32(&bars->p_full[i][1])};
-    uint32_t sc = 0;                                       // softmax steps done = PVs requested so far
+    const uint32_t bar_o[2] = {smem_u32(&bars->o_full[i][0]), smem_u32(&bars->o_full[i][1])};
+    uint32_t sc = 0;                                       // list entries done by this warpgroup
     bool ok = true;
     PBS_TRACE_DECL;
 
@@ -534,7 +522,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int32_t* ibase = p.idx + (int64_t)bh * p.S;
       float m_used = -CUDART_INF_F;                        // scaled (log2) max the exponents refer to
       float l = 0.f;
-      uint32_t steps = 0;                                  // softmax steps of this item
+      uint32_t steps = 0;                                  // entries of this item done
 
       uint32_t ent_next = n > 0 ? lst[0] : 0u;
       for (int e = 0; e < n && ok; ++e) {
@@ -553,118 +541,105 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           __syncwarp();
         }
-        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 0);
-        ok = __all_sync(0xffffffffu, wait_bar(bar_s, sc & 1u, ctl, p.status, 9));
-        if (!ok) break;
-        tc_fence_after();
-        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 1);
 
-        // Masks of this tile for the 64 columns starting at col0 (compile-time), applied in both
-        // passes: keys of the own segment that lie after the query, and 64x64 sub-blocks that were
-        // not selected (block_size 64 only).
-        const bool drop_half[2] = {p.bs == 64 && !((bits >> (2 * (row >> 6) + 0)) & 1u),
-                                   p.bs == 64 && !((bits >> (2 * (row >> 6) + 1)) & 1u)};
-        auto mask64 = [&](float (&v)[64], int half) {
+        // Two half-steps of 64 keys, each an ordinary online-softmax step on its own 64 columns of S.
+#pragma unroll
+        for (int hs = 0; hs < 2; ++hs) {
+          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 0);
+          ok = __all_sync(0xffffffffu, wait_bar(bar_s[hs], sc & 1u, ctl, p.status, 9));
+          if (!ok) break;
+          tc_fence_after();
+          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 1);
+          const uint32_t s_addr = tmem_S[i] + lane_off + 64 * hs;
+
+          // S_h is read from TMEM once and stays in registers for the maximum and the exponentiation.
+          uint32_t sr[2][32];
+          tmem_ld32(s_addr, sr[0]);
+          tmem_ld32(s_addr + 32, sr[1]);
+          tmem_wait_ld();
+          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[0][0]);
+          // masks: keys of the own segment that lie after the query; with block_size 64 the 64x64
+          // sub-block (query half, key half) may not be selected
           if (elem_mask) {
 #pragma unroll
             for (int c = 0; c < 64; ++c)
-              if (kidx[64 * half + c] > qpos) v[c] = -CUDART_INF_F;
+              if (kidx[64 * hs + c] > qpos) v[c] = -CUDART_INF_F;
           }
-          if (drop_half[half]) {
+          if (p.bs == 64 && !((bits >> (2 * (row >> 6) + hs)) & 1u)) {
 #pragma unroll
             for (int c = 0; c < 64; ++c) v[c] = -CUDART_INF_F;
           }
-        };
-        // S is read from TMEM once (a load round trip costs several hundred cycles) and stays in
-        // registers for both the maximum and the exponentiation.
-        uint32_t sr[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[i] + lane_off + 32 * c, sr[c]);
-        tmem_wait_ld();
-        float mx[4];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float (&v)[64] = *reinterpret_cast<float (*)[64]>(&sr[2 * half][0]);
-          mask64(v, half);
+          float mx[2];
 #pragma unroll
           for (int a = 0; a < 2; ++a) {
             float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
 #pragma unroll
             for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
-            mx[2 * half + a] = fmaxf(m, v[32 * a + 31]);
+            mx[a] = fmaxf(m, v[32 * a + 31]);
           }
-        }
-        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2e;
-        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 2);
+          const float mt = fmaxf(mx[0], mx[1]) * p.scale_log2e;
+          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 2);
 
-        float alpha = 1.f;
-        if (mt > m_used + kRescaleThreshold) {             // also the first finite maximum
-          alpha = ex2(m_used - mt);                        // 0 when m_used is -inf
-          m_used = mt;
-          l *= alpha;
-        }
-        const bool rescale = steps > 0 && __any_sync(0xffffffffu, alpha != 1.f);
-        if (rescale) {
-          // O_i holds the sum up to the previous step: wait for that PV, then scale in place
-          ok = __all_sync(0xffffffffu, wait_bar(bar_o, (sc - 1u) & 1u, ctl, p.status, 10));
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st16(tmem_O[i] + lane_off + c * 16, o);
+          float alpha = 1.f;
+          if (mt > m_used + kRescaleThreshold) {           // also the first finite maximum
+            alpha = ex2(m_used - mt);                      // 0 when m_used is -inf
+            m_used = mt;
+            l *= alpha;
           }
-        }
-        // The warps of the two query tiles that share a scheduler (same wq) would otherwise
-        // exponentiate at the same time, each at half the special-function rate, and both tiles
-        // would finish late; with a turn each, one tile's P is ready a whole phase earlier and the
-        // two tiles drift into opposite phases (one exponentiates while the other's MMAs run).
-        if (lane == 0) {
-          int spins = 0;
-          while (atomicCAS(&ctl->xu_lock[wq], 0, 1) != 0 && ++spins < (1 << 16)) __nanosleep(32);
-        }
-        __syncwarp();
-        const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
-        const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
-        const float2 nm2 = make_float2(-m_eff, -m_eff);
-        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        // P goes back in four stores of 32 keys (16 TMEM columns each) and is handed to the MMA
-        // issuer in two halves of 64 keys, so O += P V starts on the first half while the second is
-        // still being exponentiated.  The first half's stores are awaited only after the third
-        // quarter has been computed, which hides their round trip.
-        const float* sv = reinterpret_cast<const float*>(&sr[0][0]);
-        uint32_t pk[16];
+          const bool rescale = (steps > 0 || hs == 1) && __any_sync(0xffffffffu, alpha != 1.f);
+          if (rescale) {
+            // O_i holds the sum up to the previous half-step: wait for that P V, then scale in place.
+            // Half 0 follows the second half of the previous entry, half 1 the first half of this one.
+            const uint32_t par = hs == 0 ? ((sc - 1u) & 1u) : (sc & 1u);
+            ok = __all_sync(0xffffffffu, wait_bar(bar_o[hs ^ 1], par, ctl, p.status, 10));
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+            for (int c = 0; c < D / 16; ++c) {
+              uint32_t o[16];
+              tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
+              tmem_wait_ld();
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int col = 32 * q + 2 * c;
-            const float2 x = __ffma2_rn(make_float2(sv[col], sv[col + 1]), sc2, nm2);
-            // one pair in kPolyEvery is exponentiated on the FMA pipe, the rest on the special-function unit
-            const float2 ex = (kPolyEvery > 0 && c % (kPolyEvery > 0 ? kPolyEvery : 1) == kPolyEvery - 1)
-                                  ? exp2_fma(x) : make_float2(ex2(x.x), ex2(x.y));
-            acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
-            pk[c] = PackP<DT>::pack(ex.x, ex.y);
+              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+              tmem_st16(tmem_O[i] + lane_off + c * 16, o);
+            }
           }
-          if (q == 2) {
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar_p[0]);
-            if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3);
+          // The warps of the two query tiles that share a scheduler (same wq) would otherwise
+          // exponentiate at the same time, each at half the special-function rate, and both tiles
+          // would finish late; with a turn each, one tile's P is ready a whole phase earlier and
+          // the two tiles settle into opposite phases.
+          if (lane == 0) {
+            int spins = 0;
+            while (atomicCAS(&ctl->xu_lock[wq], 0, 1) != 0 && ++spins < (1 << 16)) __nanosleep(32);
           }
-          tmem_st16(tmem_S[i] + lane_off + 16 * q, pk);
+          __syncwarp();
+          const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
+          const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
+          const float2 nm2 = make_float2(-m_eff, -m_eff);
+          float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+          // P_h goes back over the first 32 columns of S_h in two stores of 32 keys
+          uint32_t pk[16];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int col = 32 * q + 2 * c;
+              const float2 x = __ffma2_rn(make_float2(v[col], v[col + 1]), sc2, nm2);
+              const float2 ex = make_float2(ex2(x.x), ex2(x.y));
+              acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
+              pk[c] = PackP<DT>::pack(ex.x, ex.y);
+            }
+            tmem_st16(s_addr + 16 * q, pk);
+          }
+          __syncwarp();
+          if (lane == 0) atomicExch(&ctl->xu_lock[wq], 0);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_p[hs]);
+          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3 + hs);
+          l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
         }
-        __syncwarp();
-        if (lane == 0) atomicExch(&ctl->xu_lock[wq], 0);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar_p[1]);
-        if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 4);
-        l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
+        if (!ok) break;
         ++sc;
         ++steps;
       }
@@ -672,7 +647,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
       // epilogue: O / l in the input dtype, original token order (queries are not permuted)
       if (steps > 0) {
-        ok = __all_sync(0xffffffffu, wait_bar(bar_o, (sc - 1u) & 1u, ctl, p.status, 11));
+        ok = __all_sync(0xffffffffu, wait_bar(bar_o[1], (sc - 1u) & 1u, ctl, p.status, 11));
         if (!ok) break;
         tc_fence_after();
       }
