@@ -230,7 +230,6 @@ struct Params {
 struct Ctl {
   uint32_t tmem_base;
   volatile int abort_flag;
-  int xu_lock[4];   // one per scheduler: which softmax warp may use the special-function unit
 };
 
 // Bounded wait: false when the CTA is aborting (this wait or another one ran out of time).
@@ -297,7 +296,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 2); }
     for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 2); }
     ctl->abort_flag = 0;
-    for (int i = 0; i < 4; ++i) ctl->xu_lock[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -604,15 +602,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               tmem_st16(tmem_O[i] + lane_off + c * 16, o);
             }
           }
-          // The warps of the two query tiles that share a scheduler (same wq) would otherwise
-          // exponentiate at the same time, each at half the special-function rate, and both tiles
-          // would finish late; with a turn each, one tile's P is ready a whole phase earlier and
-          // the two tiles settle into opposite phases.
-          if (lane == 0) {
-            int spins = 0;
-            while (atomicCAS(&ctl->xu_lock[wq], 0, 1) != 0 && ++spins < (1 << 16)) __nanosleep(32);
-          }
-          __syncwarp();
           const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
           const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
           const float2 nm2 = make_float2(-m_eff, -m_eff);
@@ -631,8 +620,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             tmem_st16(s_addr + 16 * q, pk);
           }
-          __syncwarp();
-          if (lane == 0) atomicExch(&ctl->xu_lock[wq], 0);
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(bar_p[hs]);
