@@ -10,15 +10,19 @@
 // tiles that either query tile selected.  A persistent CTA (one per SM) walks its items with
 // twelve warps in four roles:
 //   warp 0      TMA producer: Q tiles, then K and V tiles of the list into two 2-deep rings
-//   warps 1, 3  MMA issuers, one per query tile: S_i = Q_i K^T (SS, both operands K-major, 128B
-//               swizzle) and O_i += P_i V (TS: P read from TMEM, V MN-major from shared memory)
-//   warp 2      owns the TMEM allocation (all 512 columns: S0 S1 O0 O1, 128 columns each)
-//   warps 4-7   softmax of query tile 0: tcgen05.ld S, mask, row max / exp2 / row sum, P written
-//   warps 8-11  softmax of query tile 1  back over the first 64 columns of S as packed 16-bit
-//                             pairs; lazy rescale of O in TMEM; final O / l epilogue to global
-// Each issuer runs PV_i(e), QK_i(e+1) per list entry, so one tile's softmax overlaps the other
-// tile's MMAs and one issuer's barrier bookkeeping overlaps the other issuer's MMAs.  Every wait on an mbarrier is bounded; when one runs out the CTA
-// raises a flag, all roles leave their loops, TMEM is freed and status[0] tells the host.
+//   warps 1, 3  MMA issuers, one per query tile.  A 128-key tile is two half-steps of 64 keys with
+//               their own 64 TMEM columns: S_h = Q K_h^T (SS, both operands K-major, 128B swizzle,
+//               M=128 N=64) and O += P_h V_h (TS: P_h read from TMEM, V MN-major from shared memory)
+//   warp 2      owns the TMEM allocation (all 512 columns: per query tile S_0 S_1 (64 each) and O (128))
+//   warps 4-7   softmax of query tile 0: per half-step tcgen05.ld S_h, mask, row max / exp2 / row
+//   warps 8-11  softmax of query tile 1  sum, P_h written back over the first 32 columns of S_h as
+//               packed 16-bit pairs; lazy rescale of O in TMEM; final O / l epilogue to global
+// An issuer runs, per list entry and half h: O += P_h V_h, then S_h of the next entry into the
+// columns P_h vacated.  So while a softmax warpgroup works on one half, the MMAs of the other half
+// (and of the other query tile) run, and the next S is ready when the warpgroup comes back for it.
+// One issuer's barrier bookkeeping overlaps the other issuer's MMAs.
+// Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag, all roles leave
+// their loops, TMEM is freed and status[0] tells the host.
 #include <cuda.h>
 
 #include "pbs_common.cuh"
