@@ -34,9 +34,6 @@ constexpr int kThreads = 384;
 constexpr int NK = 2;                     // K ring depth
 constexpr int NV = 2;                     // V ring depth
 constexpr uint32_t kTmemCols = 512;
-#ifndef PBS_POLY_EVERY
-#define PBS_POLY_EVERY 0
-#endif
 constexpr float kRescaleThreshold = 8.f;  // log2 units: O is rescaled only when the max grows by more
 
 // ---------------------------------------------------------------------------------------------
@@ -178,26 +175,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 __device__ __forceinline__ float ex2(float x) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-
-// 2^x for a pair of values on the FMA pipe instead of the special-function unit (16 results per
-// clock per SM; the two softmax warps of a scheduler saturate it while both exponentiate).
-// x = n + f with n = round(x) read from the low mantissa bits of x + 1.5 * 2^23; 2^f by a cubic fitted
-// on [-0.5, 0.5] (max relative error 8e-5, far below the 16-bit rounding P gets); 2^n goes into the
-// exponent field with one integer multiply-add.  x is clamped at -126.
-__device__ __forceinline__ float2 exp2_fma(float2 x) {
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 xr = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
-  const float2 nf = __fadd2_rn(xr, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
-  float2 q = __ffma2_rn(f, make_float2(0.05508868f, 0.05508868f), make_float2(0.24260405f, 0.24260405f));
-  q = __ffma2_rn(q, f, make_float2(0.69327623f, 0.69327623f));
-  q = __ffma2_rn(q, f, make_float2(0.99992895f, 0.99992895f));
-  float2 r;
-  r.x = __uint_as_float(__float_as_uint(xr.x) * 0x800000u + __float_as_uint(q.x));
-  r.y = __uint_as_float(__float_as_uint(xr.y) * 0x800000u + __float_as_uint(q.y));
   return r;
 }
 
@@ -641,11 +618,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int c = 0; c < 16; ++c) {
               const int col = 32 * q + 2 * c;
               const float2 x = __ffma2_rn(make_float2(v[col], v[col + 1]), sc2, nm2);
-#if PBS_POLY_EVERY > 0
-              const float2 ex = (c % PBS_POLY_EVERY == PBS_POLY_EVERY - 1) ? exp2_fma(x) : make_float2(ex2(x.x), ex2(x.y));
-#else
               const float2 ex = make_float2(ex2(x.x), ex2(x.y));
-#endif
               acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
               pk[c] = PackP<DT>::pack(ex.x, ex.y);
             }
