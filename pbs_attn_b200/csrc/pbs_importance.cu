@@ -20,6 +20,7 @@ constexpr int TM = 64;   // query rows per pass
 constexpr int TN = 64;   // keys per CTA
 constexpr int KC = 32;   // head-dim chunk staged in shared memory
 constexpr int LDT = TM + 4;
+constexpr int kMmaTilesPerCta = 4;   // 64-key tiles per CTA of the tensor-core logits kernel
 
 template <int DT>
 __global__ void __launch_bounds__(256)
@@ -132,30 +133,22 @@ __global__ void __launch_bounds__(256)
 logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
                   const typename Elem<DT>::T* __restrict__ k, Strides ks,
                   typename Elem<DT>::T* __restrict__ logits, float2* __restrict__ partials,
-                  int Hq, int group, int S, int D, int bs, int L, float sqrt_d) {
+                  int Hq, int group, int S, int D, int bs, int L, int ntile, float sqrt_d) {
   using E = Elem<DT>;
   using T = typename E::T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int ld = D + 8;                                    // padded row length in elements
   T* Qs = reinterpret_cast<T*>(smem_raw);                  // [128][ld]
   T* Ks = Qs + 128 * ld;                                   // [64][ld]
+  T* stage = Ks + TN * ld;                                 // [8 warps][16 rows][64 keys]
 
-  const int jt = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh % Hq;
-  const int ntile = gridDim.x;
   const T* qbase = q + (int64_t)b * qs.b + (int64_t)h * qs.h + (int64_t)(S - bs) * qs.s;
-  const T* kbase = k + (int64_t)b * ks.b + (int64_t)(h / group) * ks.h + (int64_t)jt * TN * ks.s;
-  const int nkeys = min(TN, L - jt * TN);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cpr = D / 8;                                   // 16-byte chunks per row
 
-  for (int i = threadIdx.x; i < TN * cpr; i += blockDim.x) {
-    const int r = i / cpr, c = i % cpr;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (r < nkeys) val = *reinterpret_cast<const uint4*>(kbase + (int64_t)r * ks.s + c * 8);
-    *reinterpret_cast<uint4*>(Ks + r * ld + c * 8) = val;
-  }
+  // The query rows are staged once per pass and reused for kMmaTilesPerCta key tiles.
   for (int r0 = 0; r0 < bs; r0 += 128) {
     const int nrows = min(128, bs - r0);
     __syncthreads();
@@ -164,6 +157,18 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
       uint4 val = make_uint4(0, 0, 0, 0);
       if (r < nrows) val = *reinterpret_cast<const uint4*>(qbase + (int64_t)(r0 + r) * qs.s + c * 8);
       *reinterpret_cast<uint4*>(Qs + r * ld + c * 8) = val;
+    }
+   for (int it = 0; it < kMmaTilesPerCta; ++it) {
+    const int jt = blockIdx.x * kMmaTilesPerCta + it;
+    if (jt >= ntile) break;
+    const T* kbase = k + (int64_t)b * ks.b + (int64_t)(h / group) * ks.h + (int64_t)jt * TN * ks.s;
+    const int nkeys = min(TN, L - jt * TN);
+    __syncthreads();                                       // previous tile's K fully consumed
+    for (int i = threadIdx.x; i < TN * cpr; i += blockDim.x) {
+      const int r = i / cpr, c = i % cpr;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < nkeys) val = *reinterpret_cast<const uint4*>(kbase + (int64_t)r * ks.s + c * 8);
+      *reinterpret_cast<uint4*>(Ks + r * ld + c * 8) = val;
     }
     __syncthreads();
     if (warp * 16 < nrows) {
@@ -209,19 +214,27 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
             if (8 * j + 2 * (lane & 3) + t < nkeys) z += expf(y[2 * j + t] - m);
         z += __shfl_xor_sync(0xffffffffu, z, 1);
         z += __shfl_xor_sync(0xffffffffu, z, 2);
-        if (r < bs) {
+        // the rounded logits go through a per-warp staging tile so that each row leaves as one
+        // 128-byte store instead of eight 16-byte pieces
+        T* srow = stage + (warp * 16 + (lane >> 2) + 8 * half) * TN;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int t = 0; t < 2; ++t) srow[8 * j + 2 * (lane & 3) + t] = E::cvt(y[2 * j + t]);
+        if (r < bs && (lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+      }
+      __syncwarp();
+#pragma unroll 4
+      for (int rr = 0; rr < 16; ++rr) {
+        const int r = r0 + warp * 16 + rr;
+        if (r < bs && 2 * lane < nkeys) {
           T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              const int key = 8 * j + 2 * (lane & 3) + t;
-              if (key < nkeys) dst[key] = E::cvt(y[2 * j + t]);
-            }
-          if ((lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+          *reinterpret_cast<uint32_t*>(dst + 2 * lane) = *reinterpret_cast<const uint32_t*>(stage + (warp * 16 + rr) * TN + 2 * lane);
         }
       }
+      __syncwarp();
     }
+   }
   }
 }
 
@@ -295,13 +308,13 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
   if (DT != PBS_FP32 && d.D % 16 == 0 && qs.s % 8 == 0 && ks.s % 8 == 0) {
     // 16-bit inputs: tensor cores
     auto kern = logits_mma_kernel<DT>;
-    const size_t smem = (size_t)(128 + TN) * (d.D + 8) * sizeof(T);
+    const size_t smem = ((size_t)(128 + TN) * (d.D + 8) + 8 * 16 * TN) * sizeof(T);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return cuda_fail(e, "logits_mma_kernel smem attribute");
     }
-    kern<<<dim3(ntile, BH), 256, smem, st>>>((const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq,
-                                             d.group, d.S, d.D, d.bs, d.L, sq);
+    kern<<<dim3((ntile + kMmaTilesPerCta - 1) / kMmaTilesPerCta, BH), 256, smem, st>>>(
+        (const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq, d.group, d.S, d.D, d.bs, d.L, ntile, sq);
     PBS_CUDA_CHECK_LAUNCH("logits_mma_kernel");
   } else {
     logits_kernel<DT><<<dim3(ntile, BH), 256, 0, st>>>(
