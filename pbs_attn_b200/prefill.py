@@ -263,6 +263,22 @@ class _HostPipeline:
 _HOST_PIPES: dict = {}
 
 
+def _host_chunks(Hq: int, Hkv: int, chunks: Optional[int]):
+    """Query heads per chunk and KV heads per chunk.  Default: one KV head (with its query heads) per
+    chunk; with a single KV head, one query head per chunk (the KV head is then uploaded once)."""
+    group = Hq // Hkv
+    if chunks is None:
+        chunks = Hkv if Hkv > 1 else Hq
+    if Hq % chunks:
+        raise ValueError(f"chunks={chunks} does not divide the {Hq} query heads")
+    hq_c = Hq // chunks
+    if hq_c % group == 0:
+        return chunks, hq_c, hq_c // group          # whole KV heads per chunk
+    if group % hq_c == 0:
+        return chunks, hq_c, 1                      # several chunks share one KV head
+    raise ValueError(f"chunks={chunks}: a chunk of {hq_c} query heads neither holds nor divides a KV group of {group}")
+
+
 def permuted_block_sparse_attn_fwd_host(
     query_states: torch.Tensor,
     key_states: torch.Tensor,
@@ -281,24 +297,22 @@ def permuted_block_sparse_attn_fwd_host(
     """The same call for HOST tensors (ideally pinned): q (B, Hq, S, D), k/v (B, Hkv, S, D) in CPU
     memory, result in CPU memory.
 
-    Query heads are independent, so the call is cut into ``chunks`` groups of whole KV heads and
-    pipelined over three streams: while group g is computed, group g+1 is copied in and group g-1 is
-    copied out (PCIe is full duplex), with two device staging buffers per operand.  Only the first
-    group's upload and the last group's download are exposed.  Returns after enqueueing everything;
-    synchronise (``torch.cuda.synchronize``) before reading ``out``.
+    Query heads are independent, so the call is cut into ``chunks`` groups of query heads (by default
+    one KV head with its query heads per group) and pipelined over three streams: while group g is
+    computed, group g+1 is copied in and group g-1 is copied out (PCIe is full duplex), with two device
+    staging buffers per operand.  A KV head shared by consecutive groups is uploaded once.  Only the
+    first group's upload and the last group's download are exposed.  Returns after enqueueing
+    everything; synchronise (``torch.cuda.synchronize``) before reading ``out``.
     """
     assert causal and not query_states.is_cuda
     B, Hq, S, D = query_states.shape
     Hkv = key_states.shape[1]
     assert Hq % Hkv == 0 and key_states.shape == value_states.shape and key_states.shape[2] == S
+    group = Hq // Hkv
     dev = torch.device(device if device is not None else torch.cuda.current_device())
     if dev.type != "cuda":
         dev = torch.device("cuda", torch.cuda.current_device())
-    if chunks is None:
-        chunks = Hkv
-    if Hkv % chunks:
-        raise ValueError(f"chunks={chunks} does not divide the {Hkv} KV heads")
-    hkv_c, hq_c = Hkv // chunks, Hq // chunks
+    chunks, hq_c, hkv_c = _host_chunks(Hq, Hkv, chunks)
     if out is None:
         out = torch.empty(B, Hq, S, D, dtype=query_states.dtype).pin_memory()
     key = (B, hq_c, hkv_c, S, D, query_states.dtype, dev.index)
@@ -313,32 +327,46 @@ def permuted_block_sparse_attn_fwd_host(
     start.record(main)
     pipe.copy_in.wait_event(start)
     pipe.copy_out.wait_event(start)
-    done_compute = [None, None]      # last compute that read staging slot s
-    done_out = [None, None]          # last download that read output slot s
+    q_read = [None, None]            # last compute that read q/o staging slot s
+    kv_read = [None, None]           # last compute that read k/v staging slot s
+    o_read = [None, None]            # last download that read output slot s
+    kv_slot, kv_loaded, n_kv = 0, None, 0
     for c in range(chunks):
         s = c & 1
-        qs, ks = slice(c * hq_c, (c + 1) * hq_c), slice(c * hkv_c, (c + 1) * hkv_c)
+        qs = slice(c * hq_c, (c + 1) * hq_c)
+        kv0 = (c * hq_c) // group
+        ks = slice(kv0, kv0 + hkv_c)
         with torch.cuda.stream(pipe.copy_in):
-            if done_compute[s] is not None:
-                pipe.copy_in.wait_event(done_compute[s])
-            for dst, src in ((pipe.q[s], query_states[:, qs]), (pipe.k[s], key_states[:, ks]), (pipe.v[s], value_states[:, ks])):
+            if q_read[s] is not None:
+                pipe.copy_in.wait_event(q_read[s])
+            copies = [(pipe.q[s], query_states[:, qs])]
+            if kv_loaded != kv0:                       # a KV head shared with the previous chunk stays
+                kv_slot = n_kv & 1
+                n_kv += 1
+                kv_loaded = kv0
+                if kv_read[kv_slot] is not None:
+                    pipe.copy_in.wait_event(kv_read[kv_slot])
+                copies += [(pipe.k[kv_slot], key_states[:, ks]), (pipe.v[kv_slot], value_states[:, ks])]
+            for dst, src in copies:
                 for b in range(B):
                     dst[b].copy_(src[b], non_blocking=True)
             ev_in = torch.cuda.Event()
             ev_in.record(pipe.copy_in)
         main.wait_event(ev_in)
-        if done_out[s] is not None:
-            main.wait_event(done_out[s])
-        plan.run(pipe.q[s], pipe.k[s], pipe.v[s], pipe.o[s], opt)
-        done_compute[s] = torch.cuda.Event()
-        done_compute[s].record(main)
+        if o_read[s] is not None:
+            main.wait_event(o_read[s])
+        plan.run(pipe.q[s], pipe.k[kv_slot], pipe.v[kv_slot], pipe.o[s], opt)
+        done = torch.cuda.Event()
+        done.record(main)
+        q_read[s] = done
+        kv_read[kv_slot] = done
         with torch.cuda.stream(pipe.copy_out):
-            pipe.copy_out.wait_event(done_compute[s])
+            pipe.copy_out.wait_event(done)
             for b in range(B):
                 out[b, qs].copy_(pipe.o[s][b], non_blocking=True)
-            done_out[s] = torch.cuda.Event()
-            done_out[s].record(pipe.copy_out)
-    for ev in done_out:
+            o_read[s] = torch.cuda.Event()
+            o_read[s].record(pipe.copy_out)
+    for ev in o_read:
         if ev is not None:
             main.wait_event(ev)
     return out

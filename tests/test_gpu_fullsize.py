@@ -101,3 +101,26 @@ def test_cfg3_one_kv_group_at_131072():
     dense = torch.nn.functional.scaled_dot_product_attention(q, k.expand(-1, 4, -1, -1), v.expand(-1, 4, -1, -1), is_causal=True)
     d = (dense_out.float() - dense.float()).abs()
     assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3, (d.max().item(), d.mean().item())
+
+
+@pytest.mark.parametrize("hq,hkv,d,s,dt,bs,seg,batch", [
+    (28, 4, 128, 8192, "bf16", 64, 128, 1),     # Qwen2.5-7B heads, small blocks and segments
+    (28, 4, 128, 8192, "bf16", 128, 512, 1),    # Qwen2.5-7B heads, long segments
+    (8, 2, 64, 6000, "fp16", 64, 256, 2),       # head_dim 64, fp16, ragged length, batch 2
+    (4, 4, 128, 5000, "bf16", 128, 128, 1),     # one block per segment, no GQA, ragged length
+])
+def test_sweep_shapes_tcgen05_agrees_with_generic_kernel(hq, hkv, d, s, dt, bs, seg, batch):
+    """Shapes of the Qwen sweep (task configuration 5) and the corner cases of the tcgen05 kernel:
+    structure of permutation and mask, and agreement of the two attention kernels on the same
+    permuted inputs."""
+    from pbs_attn_b200.synth import Workload
+    w = Workload("sweep", batch, hq, hkv, d, s, dt, bs, seg, 0.9, 1e6, density=0.08, sinks=4)
+    q, k, v = make_qkv(w, seed=11, device="cuda")
+    out, inter = _run(w, q, k, v)
+    _structure_checks(w, inter)
+    assert torch.isfinite(out.float()).all()
+    ref = torch.empty_like(q)
+    inter["plan"].attn_fwd(q, ref, "simt")
+    torch.cuda.synchronize()
+    dd = (out.float() - ref.float()).abs()
+    assert dd.max().item() <= 2e-2 and dd.mean().item() <= 2e-3, (dd.max().item(), dd.mean().item())

@@ -263,7 +263,7 @@ def test_host_buffer_call_equals_device_call():
     from pbs_attn_b200.prefill import permuted_block_sparse_attn_fwd, permuted_block_sparse_attn_fwd_host
     w, kwargs, stride, (q, k, v), g = load_case("llama_bf16_s4096")
     want = permuted_block_sparse_attn_fwd(q.cuda(), k.cuda(), v.cuda(), w.block_size, w.segment_size, w.threshold, True)
-    for chunks in (None, 1):
+    for chunks in (None, 1, 8):           # one KV head per chunk; everything at once; one query head per chunk
         got = permuted_block_sparse_attn_fwd_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), w.block_size,
                                                   w.segment_size, w.threshold, True, chunks=chunks)
         torch.cuda.synchronize()
