@@ -38,6 +38,10 @@ import torch  # noqa: E402
 
 from pbs_attn_b200.synth import WORKLOADS, Workload, make_qkv  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch on one GPU, from the ncu
+# captures summarised under profiles/ (bytes); other workloads have no capture.
+ATTN_KERNEL_DRAM_TRAFFIC = {"llama8b_heads_s131072": 95.19e9, "llama8b_heads_s32768": 2.09e9}
+
 METRIC = "prefill_attn_selected_block_tflops"
 UNIT = "TFLOP/s"
 CPU_SAMPLE = dict(q_heads=4, kv_heads=1, seq_len=32768)
@@ -332,7 +336,9 @@ def run_ours(args, w: Workload):
                     "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "roofline": {"kernel": "attn_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": ATTN_KERNEL_DRAM_TRAFFIC.get(w.name) if world == 1 else None,
+                         "traffic_unit": "bytes per launch (ncu, see profiles/)",
                          "peak_source": f"{peaks['source']} ({'sustained' if long_step else 'burst'})",
                          "kernel_ms": stage_ms["attention"], "kernel_ms_max_over_ranks": attn_ms_max},
             "stages": stages,

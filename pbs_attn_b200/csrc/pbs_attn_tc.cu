@@ -79,16 +79,28 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+// L2 eviction policies for the TMA loads: K/V tiles are re-read by every query group of the head
+// (keep them), Q tiles are read once (let them go first).
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
       : "memory");
 }
 
@@ -328,6 +340,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     {
       uint32_t kc = 0, vc = 0, qc[2] = {0, 0};
       bool ok = true;
+      const uint64_t pol_kv = l2_policy_evict_last(), pol_q = l2_policy_evict_first();
       for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
         const int bh = item / p.G, g = p.G - 1 - item % p.G;
         const int b = bh / p.Hq, h = bh % p.Hq;
@@ -340,7 +353,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           if (elect_one()) {
             mbar_expect_tx(bar, kTile);
             for (int kh = 0; kh < KH; ++kh)
-              tma_load_4d(sbase + SM::kQ + i * kTile + kh * kSlab, &map_q, bar, kh * 64, r0, h, b);
+              tma_load_4d(sbase + SM::kQ + i * kTile + kh * kSlab, &map_q, bar, kh * 64, r0, h, b, pol_q);
           }
           ++qc[i];
         }
@@ -358,7 +371,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (elect_one()) {
               mbar_expect_tx(bar, kTile);
               for (int kh = 0; kh < KH; ++kh)
-                tma_load_3d(sbase + SM::kK + s * kTile + kh * kSlab, &map_k, bar, kh * 64, t * 128, bh);
+                tma_load_3d(sbase + SM::kK + s * kTile + kh * kSlab, &map_k, bar, kh * 64, t * 128, bh, pol_kv);
             }
             ++kc;
           }
@@ -370,7 +383,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             if (elect_one()) {
               mbar_expect_tx(bar, kTile);
               for (int kh = 0; kh < KH; ++kh)
-                tma_load_3d(sbase + SM::kV + s * kTile + kh * kSlab, &map_v, bar, kh * 64, t * 128, bh);
+                tma_load_3d(sbase + SM::kV + s * kTile + kh * kSlab, &map_v, bar, kh * 64, t * 128, bh, pol_kv);
             }
             ++vc;
           }
@@ -662,7 +675,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             w.y = PackP<DT>::pack(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
             w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
             w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 16 + j * 8) = w;
+            __stcs(reinterpret_cast<uint4*>(orow + c * 16 + j * 8), w);   // written once, not re-read here
           }
         }
       }
