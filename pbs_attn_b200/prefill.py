@@ -26,12 +26,15 @@ def _strides(t: torch.Tensor):
     return _cabi.Strides4(*t.stride())
 
 
-def _readable(t: torch.Tensor) -> torch.Tensor:
+def _readable(t: torch.Tensor, need_distinct_heads: bool = False) -> torch.Tensor:
     """Returns ``t`` if the kernels can read it in place (unit head-dim stride, 16-byte aligned
     rows), else a contiguous copy."""
     e = t.element_size()
     ok = (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and t.stride(2) > 0
           and all((s * e) % 16 == 0 and s >= 0 for s in t.stride()[:3]))
+    if ok and need_distinct_heads:
+        # the TMA descriptor of the query tensor cannot describe broadcast (stride-0) batch / head dims
+        ok = all(st > 0 or n == 1 for st, n in zip(t.stride()[:2], t.shape[:2]))
     return t if ok else t.contiguous()
 
 
@@ -234,7 +237,7 @@ def permuted_block_sparse_attn_fwd(
         raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
     assert segment_size % block_size == 0, "segment_size must be a multiple of block_size"
 
-    q = _readable(query_states)
+    q = _readable(query_states, need_distinct_heads=True)
     k = _readable(key_states)
     v = _readable(value_states)
     plan = get_plan(q, num_kv_heads, block_size, segment_size)
