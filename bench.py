@@ -40,7 +40,7 @@ from pbs_attn_b200.synth import WORKLOADS, Workload, make_qkv  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch on one GPU, from the ncu
 # captures summarised under profiles/ (bytes); other workloads have no capture.
-ATTN_KERNEL_DRAM_TRAFFIC = {"llama8b_heads_s131072": 95.19e9, "llama8b_heads_s32768": 2.09e9}
+ATTN_KERNEL_DRAM_TRAFFIC = {"llama8b_heads_s131072": 20.20e9}
 
 METRIC = "prefill_attn_selected_block_tflops"
 UNIT = "TFLOP/s"

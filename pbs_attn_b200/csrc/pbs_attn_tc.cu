@@ -248,6 +248,23 @@ struct Ctl {
   volatile int abort_flag;
 };
 
+// Work order.  Within a head the query groups are taken in the order G-1, 0, G-2, 1, ... and a CTA
+// takes two consecutive positions at a time, i.e. a long group followed by the short group that
+// complements it: every such pair has the same number of key tiles (2G + 2 in the dense case), so
+// (a) the CTAs stay balanced without a dynamic queue and (b) all CTAs start their long group at the
+// same time and walk up the head's key range together -- a K/V tile is then fetched from HBM once
+// and served to the other CTAs from L2, instead of every CTA sweeping at its own position.
+// n-th item of this CTA -> position in that order, or -1 past the end.
+__device__ __forceinline__ int item_position(int n, int n_items) {
+  const int pos = 2 * ((int)blockIdx.x + (n >> 1) * (int)gridDim.x) + (n & 1);
+  return pos < n_items ? pos : -1;
+}
+__device__ __forceinline__ void item_decode(int pos, int G, int& bh, int& g) {
+  bh = pos / G;
+  const int r = pos % G;
+  g = (r & 1) ? (r >> 1) : (G - 1 - (r >> 1));
+}
+
 // Bounded wait: false when the CTA is aborting (this wait or another one ran out of time).
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctl* ctl, int32_t* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -341,8 +358,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t kc = 0, vc = 0, qc[2] = {0, 0};
       bool ok = true;
       const uint64_t pol_kv = l2_policy_evict_last(), pol_q = l2_policy_evict_first();
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-        const int bh = item / p.G, g = p.G - 1 - item % p.G;
+      for (int it = 0, pos; (pos = item_position(it, p.n_items)) >= 0 && ok; ++it) {
+        int bh, g;
+        item_decode(pos, p.G, bh, g);
         const int b = bh / p.Hq, h = bh % p.Hq;
         for (int i = 0; i < 2 && ok; ++i) {
           const int r0 = g * 256 + i * 128;
@@ -436,8 +454,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_commit(bar_ofull[h]);
       };
 
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-        const int bh = item / p.G, g = p.G - 1 - item % p.G;
+      for (int it = 0, pos; (pos = item_position(it, p.n_items)) >= 0 && ok; ++it) {
+        int bh, g;
+        item_decode(pos, p.G, bh, g);
         const int n = p.count[(int64_t)bh * p.G + g];
         const uint32_t* lst = p.list + ((int64_t)bh * p.G + g) * p.T;
         const bool have = g * 256 + i * 128 < p.S;
@@ -526,8 +545,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     bool ok = true;
     PBS_TRACE_DECL;
 
-    for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
-      const int bh = item / p.G, g = p.G - 1 - item % p.G;
+    for (int it = 0, pos; (pos = item_position(it, p.n_items)) >= 0 && ok; ++it) {
+      int bh, g;
+      item_decode(pos, p.G, bh, g);
       const int r0 = g * 256 + i * 128;
       if (r0 >= p.S) continue;
       const int b = bh / p.Hq, h = bh % p.Hq;
@@ -768,7 +788,8 @@ int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void*
   const int smem = Smem<D>::kTotal;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (ce != cudaSuccess) return cuda_fail(ce, "attn_tc_kernel smem attribute");
-  const int grid = p.n_items < sm_count ? p.n_items : sm_count;
+  const int pairs = (p.n_items + 1) / 2;
+  const int grid = pairs < sm_count ? pairs : sm_count;
   kern<<<grid, kThreads, smem, st>>>(mq, mk, mv, p);
   PBS_CUDA_CHECK_LAUNCH("attn_tc_kernel");
   return PBS_OK;
