@@ -96,6 +96,11 @@ typedef struct {
   int32_t query_pool_mode;         /* pbs_pool_t                                             */
   int32_t key_pool_mode;           /* pbs_pool_t                                             */
   int32_t attn_impl;               /* pbs_attn_impl_t                                        */
+  int32_t no_permutation;          /* 1: keys stay in place (identity order); with segment_size ==
+                                      block_size and diagonal_candidates this is the reference's
+                                      MeanPooling baseline (pbs_attn/baselines/MeanPooling.py:43-58)   */
+  int32_t diagonal_candidates;     /* 1: the q block's own kv block is a selection candidate too
+                                      (block-level causal mask incl. the diagonal, MeanPooling.py:43-48) */
 } pbs_options_t;
 
 const char* pbs_last_error_string(void);

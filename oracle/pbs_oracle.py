@@ -246,3 +246,45 @@ def permuted_block_sparse_attn_fwd(q, k, v, block_size, segment_size, threshold,
     perm_v = gather_rows(v, idx)
     out = sparse_attention(q, perm_k, perm_v, idx, mask, block_size)
     return OracleResult(out, idx, mask, scores, imp)
+
+
+# --------------------------------------------------------------------------- MeanPooling baseline
+def meanpooling_block_mask(q, k, block_size, threshold, force_select_first_block=True,
+                           force_select_current_block=True, stable=True):
+    """Block mask and pooled scores of the reference's MeanPooling baseline.
+
+    pbs_attn/baselines/MeanPooling.py:24-58: zero padding to a block multiple, a
+    block-level causal mask that INCLUDES the diagonal, pooled-score softmax and
+    threshold selection (pbs_attn/src/utils.py:6-86), then kv block 0 and the
+    diagonal block forced on.  Keys are not permuted.
+    """
+    S = q.shape[2]
+    nb = (S + block_size - 1) // block_size
+    causal_blocks = torch.tril(torch.ones(nb, nb, dtype=torch.bool))
+    scores = pooled_block_scores(q, k, block_size, causal_blocks)
+    mask = select_blocks(scores, threshold, stable)
+    if force_select_first_block:
+        mask[..., 0] = True
+    if force_select_current_block:
+        mask = mask | torch.eye(nb, dtype=torch.bool)[None, None]
+    return mask, scores
+
+
+def meanpooling_prefill(q, k, v, block_size=128, threshold=0.9, force_select_first_block=True,
+                        stable=True) -> OracleResult:
+    """pbs_attn/baselines/MeanPooling.py:7-111 with ``causal=True`` and the diagonal block forced.
+
+    The reference hands its block mask to an external block-sparse flash-attention
+    library with ``is_causal=True`` (MeanPooling.py:92-106): every selected block is
+    attended, element-causally on the diagonal.  That library is not part of the
+    reference project, so the attention itself is restated from its contract:
+    softmax over the selected blocks' visible keys, the same arithmetic as
+    ``sparse_attention`` with the identity permutation.
+    """
+    B, Hq, S, D = q.shape
+    n_rep = Hq // k.shape[1]
+    k, v = repeat_kv(k, n_rep), repeat_kv(v, n_rep)        # the baseline asserts Hq == Hkv (MeanPooling.py:21)
+    mask, scores = meanpooling_block_mask(q, k, block_size, threshold, force_select_first_block, True, stable)
+    idx = torch.arange(S).view(1, 1, S).expand(B, Hq, S)
+    out = sparse_attention(q, k, v, idx, mask, block_size)
+    return OracleResult(out, idx, mask, scores, None)

@@ -2,6 +2,7 @@
 from pbs_attn_b200.hf_patch import (  # noqa: F401
     apply_patch_with_prefill,
     apply_rotary_pos_emb,
+    get_meanpooling_prefill,
     get_permuted_block_sparse_attn_fwd,
     get_supported_model_types,
     is_model_supported,

@@ -37,7 +37,8 @@ class Scratch(C.Structure):
 class Options(C.Structure):
     _fields_ = [("threshold_per_head", C.c_void_p), ("threshold", C.c_float), ("select_all", C.c_int32),
                 ("force_select_first_block", C.c_int32), ("query_pool_mode", C.c_int32),
-                ("key_pool_mode", C.c_int32), ("attn_impl", C.c_int32)]
+                ("key_pool_mode", C.c_int32), ("attn_impl", C.c_int32), ("no_permutation", C.c_int32),
+                ("diagonal_candidates", C.c_int32)]
 
 
 Strides4 = C.c_int64 * 4

@@ -155,7 +155,7 @@ int pbs_build_tile_lists(const pbs_shape_t* shape, const uint8_t* block_mask, ui
   PBS_NONNULL(block_mask); PBS_NONNULL(tile_list); PBS_NONNULL(tile_count);
   const Dims d = make_dims(*shape);
   if (d.bs != 64 && d.bs != 128) { set_error("tile lists need block_size 64 or 128 (got %d)", d.bs); return PBS_ERR_UNSUPPORTED; }
-  if (d.seg % 128) { set_error("tile lists need segment_size %% 128 == 0 (got %d)", d.seg); return PBS_ERR_UNSUPPORTED; }
+  if (d.seg % 128 && !(d.seg == 64 && d.bs == 64)) { set_error("tile lists need segment_size %% 128 == 0, or 64 with block_size 64 (got %d)", d.seg); return PBS_ERR_UNSUPPORTED; }
   return launch_build_tile_lists(d, block_mask, tile_list, tile_count, (cudaStream_t)stream);
 }
 
@@ -207,9 +207,10 @@ int pbs_prefill_fwd(const pbs_shape_t* shape, const void* q, const int64_t q_str
     PBS_NONNULL(sc->block_mask);
     PBS_TRY(launch_fill_mask_ones(make_dims(attn_shape), sc->block_mask, st));
   } else {
-    PBS_TRY(pbs_key_importance(shape, q, q_strides, k, k_strides, sc->logits, sc->partials, sc->rowstats,
-                               sc->importance, stream));
-    PBS_TRY(pbs_segment_permute(shape, sc->importance, k, k_strides, v, v_strides, sc->key_indices, sc->perm_k,
+    if (!options->no_permutation)
+      PBS_TRY(pbs_key_importance(shape, q, q_strides, k, k_strides, sc->logits, sc->partials, sc->rowstats,
+                                 sc->importance, stream));
+    PBS_TRY(pbs_segment_permute(shape, options->no_permutation ? nullptr : sc->importance, k, k_strides, v, v_strides, sc->key_indices, sc->perm_k,
                                 sc->perm_v, sc->pooled_k, options->key_pool_mode, sc->first_block, stream));
     PBS_TRY(pbs_pool_queries(shape, q, q_strides, sc->pooled_q, options->query_pool_mode, stream));
     PBS_TRY(pbs_select_blocks(shape, sc->pooled_q, sc->pooled_k, sc->first_block, options, sc->block_mask, nullptr, stream));

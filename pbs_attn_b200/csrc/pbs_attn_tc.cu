@@ -809,7 +809,7 @@ extern "C" int pbs_debug_read_trace(long long* host_buf, int* counts) {
 
 bool attn_tc_supported(const Dims& d, int dt) {
   return (dt == PBS_BF16 || dt == PBS_FP16) && (d.D == 64 || d.D == 128) && (d.bs == 64 || d.bs == 128) &&
-         d.seg % 128 == 0 && (d.S + 127) / 128 <= 0xFFFF;
+         (d.seg % 128 == 0 || (d.seg == 64 && d.bs == 64)) && (d.S + 127) / 128 <= 0xFFFF;
 }
 
 int launch_attn_tc(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,

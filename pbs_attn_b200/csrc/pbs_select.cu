@@ -22,8 +22,8 @@ template <int DT>
 __global__ void __launch_bounds__(SEL_THREADS)
 select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename Elem<DT>::T* __restrict__ pooled_k,
               const int32_t* __restrict__ first_block, const float* __restrict__ thr_per_head, float thr_scalar,
-              int select_all, int force_first, uint8_t* __restrict__ mask, float* __restrict__ scores,
-              int Hq, int D, int nb, int bps, float sqrt_d, int npow2_max) {
+              int select_all, int force_first, int diag_candidates, uint8_t* __restrict__ mask,
+              float* __restrict__ scores, int Hq, int D, int nb, int bps, float sqrt_d, int npow2_max) {
   using E = Elem<DT>;
   using T = typename E::T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -37,7 +37,8 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
   const int qb = blockIdx.x;
   const int bh = blockIdx.y;
   const int h = bh % Hq;
-  const int ncand = (qb / bps) * bps;                  // kv blocks of earlier segments
+  // candidates: kv blocks of earlier segments, or (MeanPooling variant) every block up to the diagonal
+  const int ncand = diag_candidates ? qb + 1 : (qb / bps) * bps;
   uint8_t* row = mask + ((int64_t)bh * nb + qb) * nb;
   float* srow = scores ? scores + ((int64_t)bh * nb + qb) * nb : nullptr;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -236,7 +237,7 @@ int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void
     }                                                                                                         \
     kern<<<grid, SEL_THREADS, smem, st>>>((const TT*)pooled_q, (const TT*)pooled_k, first_block,              \
                                           opt.threshold_per_head, opt.threshold, opt.select_all,             \
-                                          opt.force_select_first_block, mask, scores, d.Hq, d.D, d.nb, d.bps, sq,    \
+                                          opt.force_select_first_block, opt.diagonal_candidates, mask, scores, d.Hq, d.D, d.nb, d.bps, sq,    \
                                           npow2);                                                             \
   }
   switch (dt) {

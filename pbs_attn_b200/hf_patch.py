@@ -59,6 +59,21 @@ def get_permuted_block_sparse_attn_fwd(
                    query_pool_mode=query_pool_mode, key_pool_mode=key_pool_mode)
 
 
+def get_meanpooling_prefill(block_size=128, segment_size=1024, threshold=0.9,
+                            force_select_first_block=True, force_select_current_block=True):
+    """A ``functools.partial`` over ``MeanPooling_prefill`` (block selection without permutation), the
+    counterpart of the reference factory of the same name (pbs_attn/patch/huggingface.py:43-58)."""
+    try:
+        from . import _cabi
+        from .prefill import MeanPooling_prefill as impl
+        _cabi.load()
+    except Exception as e:
+        raise RuntimeError("MeanPooling unavailable.") from e
+    return partial(impl, block_size=block_size, segment_size=segment_size, threshold=threshold, causal=True,
+                   force_select_first_block=force_select_first_block,
+                   force_select_current_block=force_select_current_block)
+
+
 def _kernel_of(prefill_fn):
     return prefill_fn.func if isinstance(prefill_fn, partial) else prefill_fn
 
@@ -66,8 +81,8 @@ def _kernel_of(prefill_fn):
 def _takes_grouped_kv(prefill_fn) -> bool:
     """True for this package's own prefill function, which maps query heads onto fewer KV heads
     itself; any other callable gets K/V repeated to the query head count like the reference does."""
-    from .prefill import permuted_block_sparse_attn_fwd
-    return _kernel_of(prefill_fn) is permuted_block_sparse_attn_fwd
+    from .prefill import MeanPooling_prefill, permuted_block_sparse_attn_fwd
+    return _kernel_of(prefill_fn) in (permuted_block_sparse_attn_fwd, MeanPooling_prefill)
 
 
 def patched_attention_forward(

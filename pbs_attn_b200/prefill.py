@@ -91,7 +91,7 @@ class Plan:
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
     def options(self, threshold, force_select_first_block=True, query_pool_mode="mean", key_pool_mode="mean",
-                attn_impl="auto") -> _cabi.Options:
+                attn_impl="auto", no_permutation=False, diagonal_candidates=False) -> _cabi.Options:
         for m in (query_pool_mode, key_pool_mode):
             if m not in _cabi.POOL:
                 raise ValueError(f"Invalid pool mode: {m}")
@@ -106,7 +106,8 @@ class Plan:
         else:
             thr = float(threshold)
         return _cabi.Options(thr_ptr, thr, select_all, int(bool(force_select_first_block)),
-                             _cabi.POOL[query_pool_mode], _cabi.POOL[key_pool_mode], _cabi.ATTN_IMPL[attn_impl])
+                             _cabi.POOL[query_pool_mode], _cabi.POOL[key_pool_mode], _cabi.ATTN_IMPL[attn_impl],
+                             int(bool(no_permutation)), int(bool(diagonal_candidates)))
 
     def check_status(self):
         """Synchronises and raises if a kernel reported a device-side error."""
@@ -242,6 +243,56 @@ def permuted_block_sparse_attn_fwd(
     v = _readable(value_states)
     plan = get_plan(q, num_kv_heads, block_size, segment_size)
     opt = plan.options(threshold, force_select_first_block, query_pool_mode, key_pool_mode, attn_impl)
+    out = torch.empty_like(q)
+    plan.run(q, k, v, out, opt)
+    if intermediates is not None:
+        intermediates["plan"] = plan
+        intermediates["key_indices"] = plan.key_indices
+        intermediates["block_mask"] = plan.block_mask
+    if os.environ.get("PBS_B200_CHECK_STATUS") == "1":
+        plan.check_status()
+    return out
+
+
+def MeanPooling_prefill(
+    query_states: torch.Tensor,
+    key_states: torch.Tensor,
+    value_states: torch.Tensor,
+    block_size: int = 128,
+    segment_size: int = 1024,
+    threshold: float = 0.9,
+    causal: bool = True,
+    force_select_first_block: bool = True,
+    force_select_current_block: bool = True,
+    attn_impl: str = "auto",
+    intermediates: Optional[dict] = None,
+):
+    """The reference's mean-pooling block selection WITHOUT key permutation, on the same kernels.
+
+    Same arguments and result as pbs_attn/baselines/MeanPooling.py:7-111: every q block scores
+    all kv blocks up to and including its own, keeps the top blocks reaching ``threshold``, always
+    keeps kv block 0 (``force_select_first_block``) and its own block, and attends causally.
+    ``segment_size`` is accepted and unused, as in the reference.  Implemented as the permuted
+    pipeline with identity key order, one block per segment and the diagonal block among the
+    candidates.  Additive: batch > 1 and Hkv < Hq are accepted; ``force_select_current_block=False``
+    and ``causal=False`` are not supported (the attention kernel always needs the diagonal block).
+    """
+    batch_size, num_q_heads, q_len, head_dim = query_states.shape
+    _, num_kv_heads, kv_len, _ = key_states.shape
+    assert num_q_heads % num_kv_heads == 0
+    assert q_len == kv_len, "Only support prefilling for now, q_len: {}, kv_len: {}".format(q_len, kv_len)
+    if not causal or not force_select_current_block:
+        raise NotImplementedError("MeanPooling_prefill on the CUDA library is causal and always keeps the current block")
+    if not query_states.is_cuda:
+        raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
+    q = _readable(query_states, need_distinct_heads=True)
+    k = _readable(key_states)
+    v = _readable(value_states)
+    plan = get_plan(q, num_kv_heads, block_size, block_size)
+    if not isinstance(threshold, torch.Tensor):
+        threshold = float(threshold)        # the baseline has no "int 1 selects everything" rule
+    opt = plan.options(threshold, force_select_first_block, "mean", "mean", attn_impl,
+                       no_permutation=True, diagonal_candidates=True)
     out = torch.empty_like(q)
     plan.run(q, k, v, out, opt)
     if intermediates is not None:

@@ -28,3 +28,11 @@ CASES = {
     # q_len <= segment_size: the dense fallback
     "short_dense": (Workload("short_dense", 1, 4, 2, 64, 200, "bf16", 64, 256, 0.9, 1e4), 13, {}, 1),
 }
+
+# MeanPooling baseline (selection without permutation): segment_size is unused by it
+MEANPOOLING_CASES = {
+    "meanpool_bf16_s2048": (Workload("meanpool_bf16_s2048", 1, 4, 1, 128, 2048, "bf16", 128, 128, 0.9, 5e5, sinks=4), 21, {}, 8),
+    "meanpool_bf16_bs64_s1500": (Workload("meanpool_bf16_bs64_s1500", 1, 4, 2, 128, 1500, "bf16", 64, 64, 0.8, 1e6, density=0.05), 22, {}, 4),
+    "meanpool_fp32_s1000": (Workload("meanpool_fp32_s1000", 2, 2, 2, 64, 1000, "fp32", 64, 64, 0.9, 1e4), 23,
+                            {"force_select_first_block": False}, 4),
+}

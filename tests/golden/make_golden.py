@@ -3,7 +3,7 @@
 Run once, in a container that has the reference checked out (it is imported
 from REFERENCE_ROOT, default /root/reference, and is not needed afterwards):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [--meanpooling-only]
 
 Per case two runs are stored: ``*_ref`` from the reference as it is (its sorts
 are non-stable: the order of tied items is implementation defined) and
@@ -89,13 +89,81 @@ def run_reference(ref_pbs, q, k, v, w, kwargs):
     return out, idx, mask, scores
 
 
+class _BlockSparseAttnStub:
+    """Stands in for the external ``block_sparse_attn`` library the MeanPooling baseline imports
+    (it is not part of the reference project).  ``block_sparse_attn_func`` keeps the block mask the
+    reference computed and evaluates the library's documented contract in fp32: softmax over the
+    keys of the selected blocks, element-causal, result rounded to the input dtype."""
+
+    def __init__(self):
+        self.block_mask = None
+
+    def block_sparse_attn_func(self, q, k, v, cu_q, cu_k, head_mask_type, streaming_info, block_mask,
+                               max_q, max_k, p_dropout=0.0, deterministic=True, is_causal=True):
+        assert is_causal and p_dropout == 0.0 and streaming_info is None
+        self.block_mask = block_mask.clone()
+        S, H, D = q.shape
+        bs = (S + block_mask.shape[-1] - 1) // block_mask.shape[-1]
+        bs = 1 << (bs - 1).bit_length()                       # block sizes in the cases are powers of two
+        elem = block_mask[0].repeat_interleave(bs, dim=-2).repeat_interleave(bs, dim=-1)[:, :S, :S]
+        elem = elem & torch.tril(torch.ones(S, S, dtype=torch.bool))
+        logits = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / (D ** 0.5)
+        p = torch.softmax(logits.masked_fill(~elem, float("-inf")), dim=-1)
+        return torch.einsum("hqk,khd->qhd", p, v.float()).to(q.dtype)
+
+
+def make_meanpooling(make_qkv, cases):
+    """MeanPooling fixtures: the reference's own MeanPooling_prefill (pbs_attn/baselines/MeanPooling.py)
+    run unmodified with the stub above in place of the external attention library."""
+    import types
+    stub = _BlockSparseAttnStub()
+    mod = types.ModuleType("block_sparse_attn")
+    mod.block_sparse_attn_func = stub.block_sparse_attn_func
+    sys.modules["block_sparse_attn"] = mod
+    sys.path.insert(0, REFERENCE_ROOT)
+    try:
+        import pbs_attn.baselines.MeanPooling as ref_mp
+        import pbs_attn.src.utils as ref_utils
+        assert os.path.abspath(ref_mp.__file__).startswith(os.path.abspath(REFERENCE_ROOT)), ref_mp.__file__
+    finally:
+        sys.path.remove(REFERENCE_ROOT)
+    for name, (w, seed, kwargs, stride) in cases.items():
+        q, k, v = make_qkv(w, seed)
+        n_rep = w.q_heads // w.kv_heads
+        kr, vr = k.repeat_interleave(n_rep, dim=1), v.repeat_interleave(n_rep, dim=1)
+        rec = {"inputs_sha256": np.array(sha_inputs(q, k, v)), "row_stride": np.array(stride)}
+        for tag, ctx in (("ref", contextlib.nullcontext()), ("stable", stable_sorts())):
+            outs, masks = [], []
+            with ctx:
+                for b in range(w.batch):                      # the baseline asserts batch size 1
+                    outs.append(ref_mp.MeanPooling_prefill(q[b:b + 1], kr[b:b + 1], vr[b:b + 1], block_size=w.block_size,
+                                                           threshold=w.threshold, **kwargs))
+                    masks.append(stub.block_mask)
+            out, mask = torch.cat(outs), torch.cat(masks)
+            rec[f"out_{tag}"] = raw(out[:, :, ::stride, :])
+            rec[f"mask_{tag}"] = np.packbits(mask.numpy(), axis=-1)
+        # the pooled scores, from the reference's own scoring function on the same padded inputs
+        pad = (-w.seq_len) % w.block_size
+        qp = torch.nn.functional.pad(q, (0, 0, 0, pad)); kp = torch.nn.functional.pad(kr, (0, 0, 0, pad))
+        nb = (w.seq_len + pad) // w.block_size
+        rec["scores"] = ref_utils.block_pooled_attn(qp, kp, w.block_size, torch.tril(torch.ones(nb, nb, dtype=torch.bool))).numpy()
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **rec)
+        print(f"{name}: {os.path.getsize(path) / 1024:.0f} KiB, ref==stable mask: "
+              f"{np.array_equal(rec['mask_ref'], rec['mask_stable'])}")
+
+
 def main():
     sys.path.insert(0, ROOT)
     from pbs_attn_b200.synth import make_qkv
     sys.path.insert(0, HERE)
-    from cases import CASES
+    from cases import CASES, MEANPOOLING_CASES
     ref_pbs = _import_reference()
     torch.set_num_threads(os.cpu_count() or 1)
+    if "--meanpooling-only" in sys.argv:
+        make_meanpooling(make_qkv, MEANPOOLING_CASES)
+        return
+    make_meanpooling(make_qkv, MEANPOOLING_CASES)
     for name, (w, seed, kwargs, stride) in CASES.items():
         q, k, v = make_qkv(w, seed)
         rec = {"inputs_sha256": np.array(sha_inputs(q, k, v)), "row_stride": np.array(stride)}

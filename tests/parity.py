@@ -5,7 +5,7 @@ import os
 import numpy as np
 import torch
 
-from cases import CASES
+from cases import CASES, MEANPOOLING_CASES
 from pbs_attn_b200.synth import make_qkv
 
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -15,7 +15,7 @@ TOL = {torch.bfloat16: (2e-2, 2e-3), torch.float16: (2e-2, 2e-3), torch.float32:
 
 
 def load_case(name):
-    w, seed, kwargs, stride = CASES[name]
+    w, seed, kwargs, stride = (CASES.get(name) or MEANPOOLING_CASES[name])
     q, k, v = make_qkv(w, seed)
     g = dict(np.load(os.path.join(GOLDEN_DIR, name + ".npz")))
     h = hashlib.sha256()

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from cases import CASES
+from cases import CASES, MEANPOOLING_CASES
 from oracle import pbs_oracle
 from parity import assert_close_out, golden_mask, golden_out, load_case
 
@@ -69,3 +69,20 @@ def test_oracle_threshold_never_reached_keeps_only_forced_blocks():
     same = (qb // bps) == (kb // bps)
     forced = same[None, None] | pbs_oracle.first_token_blocks(r.key_indices, w.seq_len, w.block_size)
     assert torch.equal(r.block_mask, forced.expand_as(r.block_mask))
+
+
+@pytest.mark.parametrize("name", list(MEANPOOLING_CASES))
+def test_meanpooling_oracle_equals_reference(name):
+    """The MeanPooling restatement against the reference's own MeanPooling_prefill (run with a stub
+    for the external attention library it imports): block mask and pooled scores bit-exact, output
+    within tolerance of the stub's fp32 attention."""
+    w, kwargs, stride, (q, k, v), g = load_case(name)
+    r = pbs_oracle.meanpooling_prefill(q, k, v, w.block_size, w.threshold, stable=True, **kwargs)
+    nb = -(-w.seq_len // w.block_size)
+    assert torch.equal(r.block_mask, golden_mask(g, "stable", nb))
+    assert torch.equal(r.block_mask, golden_mask(g, "ref", nb))
+    assert np.array_equal(r.block_scores.numpy(), g["scores"])
+    assert_close_out(r.out[:, :, ::stride, :], golden_out(g, "stable", w.torch_dtype), w.torch_dtype, name)
+    eye = torch.eye(nb, dtype=torch.bool)
+    assert (r.block_mask & eye).sum() == eye.sum() * w.batch * w.q_heads        # the diagonal is always on
+    assert not torch.triu(r.block_mask, diagonal=1).any()                        # nothing above it
