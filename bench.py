@@ -367,6 +367,8 @@ def main():
     ap.add_argument("--workload", default="llama8b_heads_s131072", choices=sorted(WORKLOADS))
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--threshold", type=float, default=None)
+    ap.add_argument("--heads", default=None, metavar="HQ,HKV",
+                    help="run a slice of the workload with this many query / KV heads (for profiler-sized cases)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -375,6 +377,9 @@ def main():
         w = w.with_(seq_len=args.seq_len, name=f"{w.name.rsplit('_s', 1)[0]}_s{args.seq_len}")
     if args.threshold is not None:
         w = w.with_(threshold=args.threshold)
+    if args.heads:
+        hq, hkv = (int(x) for x in args.heads.split(","))
+        w = w.with_(q_heads=hq, kv_heads=hkv, name=f"{w.name}_h{hq}x{hkv}")
     if args.impl == "reference":
         run_reference(args, w)
     else:

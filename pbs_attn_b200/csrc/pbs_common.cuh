@@ -113,6 +113,65 @@ __device__ __forceinline__ void bitonic_sort_desc(unsigned long long* keys, int 
   }
 }
 
+// The same result with E keys per thread held in registers (thread t owns keys t*E .. t*E+E-1):
+// compare-exchange distances below E stay inside a thread, distances below 32*E go through warp
+// shuffles, and only the few larger ones through shared memory.  n is a power of two with
+// E <= n <= E * blockDim.x; every thread of the block must call it.
+template <int E>
+__device__ __forceinline__ void bitonic_sort_desc_regs(unsigned long long* keys, int n) {
+  const int base = (int)threadIdx.x * E;
+  const bool active = base < n;
+  unsigned long long x[E];
+#pragma unroll
+  for (int r = 0; r < E; ++r) x[r] = active ? keys[base + r] : 0ull;
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j >= E; j >>= 1) {
+      const int tj = j / E;                                // distance of the partner thread
+      const bool take_max = ((base & j) == 0) == ((base & k) == 0);
+      if (tj >= 32) {
+        __syncthreads();
+        if (active) {
+#pragma unroll
+          for (int r = 0; r < E; ++r) keys[base + r] = x[r];
+        }
+        __syncthreads();
+        if (active) {
+#pragma unroll
+          for (int r = 0; r < E; ++r) {
+            const unsigned long long y = keys[(base + r) ^ j];
+            x[r] = take_max ? (x[r] > y ? x[r] : y) : (x[r] < y ? x[r] : y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < E; ++r) {
+          const unsigned long long y = __shfl_xor_sync(0xffffffffu, x[r], tj);
+          x[r] = take_max ? (x[r] > y ? x[r] : y) : (x[r] < y ? x[r] : y);
+        }
+      }
+    }
+#pragma unroll
+    for (int jj = E / 2; jj >= 1; jj >>= 1) {
+      if (jj <= (k >> 1)) {
+#pragma unroll
+        for (int r = 0; r < E; ++r) {
+          if ((r & jj) == 0) {
+            const bool desc = ((base + r) & k) == 0;
+            const unsigned long long a = x[r], b = x[r | jj];
+            if (desc ? (a < b) : (a > b)) { x[r] = b; x[r | jj] = a; }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (active) {
+#pragma unroll
+    for (int r = 0; r < E; ++r) keys[base + r] = x[r];
+  }
+  __syncthreads();
+}
+
 static inline int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
 // Error reporting of the C ABI (thread local message).

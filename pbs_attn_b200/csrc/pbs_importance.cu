@@ -21,6 +21,7 @@ constexpr int TN = 64;   // keys per CTA
 constexpr int KC = 32;   // head-dim chunk staged in shared memory
 constexpr int LDT = TM + 4;
 constexpr int kMmaTilesPerCta = 4;   // 64-key tiles per CTA of the tensor-core logits kernel
+constexpr int kStageLd = TN + 8;     // elements per row of the per-warp output staging tile
 
 template <int DT>
 __global__ void __launch_bounds__(256)
@@ -140,7 +141,7 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
   const int ld = D + 8;                                    // padded row length in elements
   T* Qs = reinterpret_cast<T*>(smem_raw);                  // [128][ld]
   T* Ks = Qs + 128 * ld;                                   // [64][ld]
-  T* stage = Ks + TN * ld;                                 // [8 warps][16 rows][64 keys]
+  T* stage = Ks + TN * ld;                                 // [8 warps][16 rows][kStageLd]
 
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh % Hq;
@@ -191,6 +192,8 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
         }
       }
       // this thread: rows lane/4 and lane/4 + 8 of the warp's 16, keys 8j + 2(lane%4), +1
+      const bool full = nkeys == TN;
+      const float rinv = 1.f / sqrt_d;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int r = r0 + warp * 16 + (lane >> 2) + 8 * half;
@@ -200,9 +203,13 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
         for (int j = 0; j < 8; ++j)
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            const int key = 8 * j + 2 * (lane & 3) + t;
-            y[2 * j + t] = E::rnd(E::rnd(acc[j][2 * half + t]) / sqrt_d);
-            if (key < nkeys) m = fmaxf(m, y[2 * j + t]);
+            // a / sqrt_d in fp32: reciprocal product corrected by one exact-remainder step, which
+            // gives the correctly rounded quotient; then the second rounding to the input type
+            const float a = E::rnd(acc[j][2 * half + t]);
+            float qv = a * rinv;
+            qv = fmaf(fmaf(-qv, sqrt_d, a), rinv, qv);
+            y[2 * j + t] = E::rnd(qv);
+            if (full || 8 * j + 2 * (lane & 3) + t < nkeys) m = fmaxf(m, y[2 * j + t]);
           }
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
@@ -211,25 +218,39 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
         for (int j = 0; j < 8; ++j)
 #pragma unroll
           for (int t = 0; t < 2; ++t)
-            if (8 * j + 2 * (lane & 3) + t < nkeys) z += expf(y[2 * j + t] - m);
+            if (full || 8 * j + 2 * (lane & 3) + t < nkeys) z += __expf(y[2 * j + t] - m);
         z += __shfl_xor_sync(0xffffffffu, z, 1);
         z += __shfl_xor_sync(0xffffffffu, z, 2);
-        // the rounded logits go through a per-warp staging tile so that each row leaves as one
-        // 128-byte store instead of eight 16-byte pieces
-        T* srow = stage + (warp * 16 + (lane >> 2) + 8 * half) * TN;
+        // the rounded logits go through a per-warp staging tile (rows padded by 8 elements, which
+        // spreads the eight rows of a store over all banks) and leave as 16-byte pieces
+        T* srow = stage + (warp * 16 + (lane >> 2) + 8 * half) * kStageLd;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-          for (int t = 0; t < 2; ++t) srow[8 * j + 2 * (lane & 3) + t] = E::cvt(y[2 * j + t]);
+        for (int j = 0; j < 8; ++j) {
+          T pair[2] = {E::cvt(y[2 * j]), E::cvt(y[2 * j + 1])};
+          *reinterpret_cast<uint32_t*>(srow + 8 * j + 2 * (lane & 3)) = *reinterpret_cast<const uint32_t*>(pair);
+        }
         if (r < bs && (lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
       }
       __syncwarp();
+      if (full) {
+        // four rows per store instruction: 8 lanes x 16 bytes cover the 64 keys of a row
+#pragma unroll
+        for (int rr = 0; rr < 16; rr += 4) {
+          const int lr = rr + (lane >> 3);
+          const int r = r0 + warp * 16 + lr;
+          if (r < bs) {
+            T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN + (lane & 7) * 8;
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage + (warp * 16 + lr) * kStageLd + (lane & 7) * 8);
+          }
+        }
+      } else {
 #pragma unroll 4
-      for (int rr = 0; rr < 16; ++rr) {
-        const int r = r0 + warp * 16 + rr;
-        if (r < bs && 2 * lane < nkeys) {
-          T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
-          *reinterpret_cast<uint32_t*>(dst + 2 * lane) = *reinterpret_cast<const uint32_t*>(stage + (warp * 16 + rr) * TN + 2 * lane);
+        for (int rr = 0; rr < 16; ++rr) {
+          const int r = r0 + warp * 16 + rr;
+          if (r < bs && 2 * lane < nkeys) {
+            T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
+            *reinterpret_cast<uint32_t*>(dst + 2 * lane) = *reinterpret_cast<const uint32_t*>(stage + (warp * 16 + rr) * kStageLd + 2 * lane);
+          }
         }
       }
       __syncwarp();
@@ -308,7 +329,7 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
   if (DT != PBS_FP32 && d.D % 16 == 0 && qs.s % 8 == 0 && ks.s % 8 == 0) {
     // 16-bit inputs: tensor cores
     auto kern = logits_mma_kernel<DT>;
-    const size_t smem = ((size_t)(128 + TN) * (d.D + 8) + 8 * 16 * TN) * sizeof(T);
+    const size_t smem = ((size_t)(128 + TN) * (d.D + 8) + 8 * 16 * kStageLd) * sizeof(T);
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return cuda_fail(e, "logits_mma_kernel smem attribute");

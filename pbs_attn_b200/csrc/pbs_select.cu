@@ -18,7 +18,8 @@ namespace {
 
 constexpr int SEL_THREADS = 256;
 
-template <int DT>
+// KPT: sort keys per thread held in registers (0: sort in shared memory, any size)
+template <int DT, int KPT>
 __global__ void __launch_bounds__(SEL_THREADS)
 select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename Elem<DT>::T* __restrict__ pooled_k,
               const int32_t* __restrict__ first_block, const float* __restrict__ thr_per_head, float thr_scalar,
@@ -57,29 +58,61 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
     for (int i = threadIdx.x; i < ncand; i += blockDim.x) row[i] = 1;
   } else if (ncand > 0) {
     while (npow2 < ncand) npow2 <<= 1;
+    if (KPT > 1 && npow2 < KPT) npow2 = KPT;
     for (int d = threadIdx.x; d < D; d += blockDim.x) pq[d] = E::ld(pooled_q + ((int64_t)bh * nb + qb) * D + d);
     __syncthreads();
-    // pooled logits: one thread per kv block; its pooled-K row is fetched with independent 16-byte
-    // loads (all in flight together -- the rows come from L2 and latency, not bandwidth, is the cost)
-    for (int kb = threadIdx.x; kb < ncand; kb += SEL_THREADS) {
-      const uint4* pk4 = reinterpret_cast<const uint4*>(pooled_k + ((int64_t)bh * nb + kb) * D);
-      constexpr int EPV = 16 / (int)sizeof(T);           // elements per 16-byte vector
-      float acc = 0.f;
-      for (int c0 = 0; c0 < D / EPV; c0 += 8) {
-        uint4 buf[8];
+    constexpr int EPV = 16 / (int)sizeof(T);             // elements per 16-byte vector
+    const int cpr = D / EPV;                             // 16-byte chunks per pooled row
+    if (cpr <= 32 && (cpr & (cpr - 1)) == 0) {
+      // pooled logits, rows shared by the lanes of a warp: lane = (row in group, chunk), so one load
+      // instruction fetches 32 / cpr whole rows as consecutive 16-byte pieces; each lane multiplies
+      // its piece with the matching piece of pooled q (kept in registers) and the partial sums are
+      // folded over the cpr lanes of a row.
+      const int chunk = lane % cpr, rpp = 32 / cpr;      // rows per warp-wide load
+      float pqr[EPV];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (c0 + j < D / EPV) buf[j] = pk4[c0 + j];
+      for (int t = 0; t < EPV; ++t) pqr[t] = pq[chunk * EPV + t];
+      constexpr int U = 4;                               // independent loads in flight per lane
+      for (int kb0 = warp * rpp; kb0 < ncand; kb0 += U * (SEL_THREADS / 32) * rpp) {
+        uint4 buf[U];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (c0 + j < D / EPV) {
-            const T* e = reinterpret_cast<const T*>(&buf[j]);
+        for (int u = 0; u < U; ++u) {
+          const int kb = kb0 + u * (SEL_THREADS / 32) * rpp + lane / cpr;
+          buf[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (kb < ncand) buf[u] = reinterpret_cast<const uint4*>(pooled_k + ((int64_t)bh * nb + kb) * D)[chunk];
+        }
 #pragma unroll
-            for (int t = 0; t < EPV; ++t) acc = fmaf(pq[(c0 + j) * EPV + t], E::ld(e + t), acc);
-          }
+        for (int u = 0; u < U; ++u) {
+          const int kb = kb0 + u * (SEL_THREADS / 32) * rpp + lane / cpr;
+          const T* e = reinterpret_cast<const T*>(&buf[u]);
+          float acc = 0.f;
+#pragma unroll
+          for (int t = 0; t < EPV; ++t) acc = fmaf(pqr[t], E::ld(e + t), acc);
+          for (int o = cpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+          if (chunk == 0 && kb < ncand) vals[kb] = E::rnd(E::rnd(acc) / sqrt_d);
         }
       }
-      vals[kb] = E::rnd(E::rnd(acc) / sqrt_d);
+    } else {
+      // generic head sizes: one thread per kv block, its pooled-K row fetched with independent loads
+      for (int kb = threadIdx.x; kb < ncand; kb += SEL_THREADS) {
+        const uint4* pk4 = reinterpret_cast<const uint4*>(pooled_k + ((int64_t)bh * nb + kb) * D);
+        float acc = 0.f;
+        for (int c0 = 0; c0 < cpr; c0 += 8) {
+          uint4 buf[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (c0 + j < cpr) buf[j] = pk4[c0 + j];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (c0 + j < cpr) {
+              const T* e = reinterpret_cast<const T*>(&buf[j]);
+#pragma unroll
+              for (int t = 0; t < EPV; ++t) acc = fmaf(pq[(c0 + j) * EPV + t], E::ld(e + t), acc);
+            }
+          }
+        }
+        vals[kb] = E::rnd(E::rnd(acc) / sqrt_d);
+      }
     }
     __syncthreads();
     // fp32 softmax over the candidates
@@ -116,7 +149,8 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
       keys[i] = key;
     }
     __syncthreads();
-    bitonic_sort_desc(keys, npow2);
+    if constexpr (KPT > 0) bitonic_sort_desc_regs<KPT>(keys, npow2);
+    else bitonic_sort_desc(keys, npow2);
     // running sum in double over the sorted probabilities; each thread owns a contiguous chunk
     const int chunk = (ncand + SEL_THREADS - 1) / SEL_THREADS;
     const int c0 = min(threadIdx.x * chunk, ncand), c1 = min(c0 + chunk, ncand);
@@ -228,17 +262,28 @@ int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void
   const size_t smem = (size_t)npow2 * 8 + (size_t)d.D * 4 + (size_t)d.nb * 4;
   dim3 grid(d.nb, d.B * d.Hq);
   const float sq = (float)sqrt((double)d.D);
-#define PBS_SEL(DT, TT)                                                                                       \
+#define PBS_SEL_E(DT, TT, EE)                                                                                 \
   {                                                                                                           \
-    auto kern = select_kernel<DT>;                                                                            \
+    auto kern = select_kernel<DT, EE>;                                                                        \
     if (smem > 48 * 1024) {                                                                                   \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
       if (e != cudaSuccess) return cuda_fail(e, "select_kernel smem attribute");                              \
     }                                                                                                         \
     kern<<<grid, SEL_THREADS, smem, st>>>((const TT*)pooled_q, (const TT*)pooled_k, first_block,              \
                                           opt.threshold_per_head, opt.threshold, opt.select_all,             \
-                                          opt.force_select_first_block, opt.diagonal_candidates, mask, scores, d.Hq, d.D, d.nb, d.bps, sq,    \
-                                          npow2);                                                             \
+                                          opt.force_select_first_block, opt.diagonal_candidates, mask,       \
+                                          scores, d.Hq, d.D, d.nb, d.bps, sq, npow2);                         \
+  }
+  // keys per thread of the register sort; beyond 16 the sort runs in shared memory
+#define PBS_SEL(DT, TT)                                                                                       \
+  {                                                                                                           \
+    const int per_thread = (npow2 + SEL_THREADS - 1) / SEL_THREADS;                                           \
+    if (per_thread <= 1) PBS_SEL_E(DT, TT, 1)                                                                 \
+    else if (per_thread == 2) PBS_SEL_E(DT, TT, 2)                                                            \
+    else if (per_thread == 4) PBS_SEL_E(DT, TT, 4)                                                            \
+    else if (per_thread == 8) PBS_SEL_E(DT, TT, 8)                                                            \
+    else if (per_thread == 16) PBS_SEL_E(DT, TT, 16)                                                          \
+    else PBS_SEL_E(DT, TT, 0)                                                                                 \
   }
   switch (dt) {
     case PBS_BF16: PBS_SEL(PBS_BF16, __nv_bfloat16) break;
@@ -246,6 +291,7 @@ int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void
     default: PBS_SEL(PBS_FP32, float)
   }
 #undef PBS_SEL
+#undef PBS_SEL_E
   PBS_CUDA_CHECK_LAUNCH("select_kernel");
   return PBS_OK;
 }
