@@ -53,6 +53,11 @@ def dense_prefill(query_states, key_states, value_states):
     return torch.nn.functional.scaled_dot_product_attention(query_states, key_states, value_states, is_causal=True)
 
 
+def no_attention(query_states, key_states, value_states):
+    """Returns the queries unchanged: the time of everything in the model except attention."""
+    return query_states
+
+
 def prefill_function(method: str, block_size: int, segment_size: int, threshold: float):
     from .hf_patch import get_meanpooling_prefill, get_permuted_block_sparse_attn_fwd
     if method == "pbs":
@@ -61,6 +66,8 @@ def prefill_function(method: str, block_size: int, segment_size: int, threshold:
         return get_meanpooling_prefill(block_size=block_size, threshold=threshold)
     if method == "dense":
         return dense_prefill
+    if method == "noattn":
+        return no_attention
     raise ValueError(method)
 
 
@@ -91,7 +98,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--arch", default="llama3.1-8b", choices=sorted(ARCHS))
     ap.add_argument("--layers", type=int, default=None, help="build only this many decoder layers")
-    ap.add_argument("--method", default="pbs", choices=["pbs", "meanpooling", "dense", "unpatched"])
+    ap.add_argument("--method", default="pbs", choices=["pbs", "meanpooling", "dense", "noattn", "unpatched"])
     ap.add_argument("--lens", default="8192,16384,32768,65536,131072")
     ap.add_argument("--block-size", type=int, default=128)
     ap.add_argument("--segment-size", type=int, default=256)
