@@ -1,4 +1,4 @@
-"""Head sharding of one prefill call across the GPUs of a node.
+"""Head (and batch) sharding of one prefill call across the GPUs of a node.
 
 Every (batch, query head) of the path is independent end to end -- own importance scores,
 permutation, block mask and attention (reference: pbs_attn/src/permute_states.py:44-56, grid of
@@ -53,6 +53,34 @@ def shard_heads(q_heads: int, kv_heads: int, rank: int, world: int) -> HeadShard
     start = part * base + min(part, extra)
     count = base + (1 if part < extra else 0)
     return HeadShard(kv * group + start, count, kv, 1)
+
+
+def shard_batch(batch: int, rank: int, world: int) -> slice:
+    """Multi-sequence prefill: whole sequences per rank, as evenly as possible (the first
+    ``batch % world`` ranks take one more); sequences are independent, so nothing is exchanged
+    while computing.  Ranks beyond the batch get an empty slice."""
+    assert 0 <= rank < world
+    base, extra = divmod(batch, world)
+    start = rank * base + min(rank, extra)
+    return slice(start, start + base + (1 if rank < extra else 0))
+
+
+def gather_batch(local_out: torch.Tensor, batch: int, group=None) -> torch.Tensor:
+    """All-gathers per-rank (B_local, Hq, S, D) outputs of ``shard_batch`` into (batch, Hq, S, D)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return local_out
+    _, H, S, D = local_out.shape
+    parts = [shard_batch(batch, r, world) for r in range(world)]
+    bmax = max(p.stop - p.start for p in parts)
+    send = torch.zeros(bmax, H, S, D, dtype=local_out.dtype, device=local_out.device)
+    send[: local_out.shape[0]] = local_out
+    recv = torch.empty(world, bmax, H, S, D, dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(recv.view(-1), send.view(-1), group=group)
+    full = torch.empty(batch, H, S, D, dtype=local_out.dtype, device=local_out.device)
+    for r, p in enumerate(parts):
+        full[p] = recv[r, : p.stop - p.start]
+    return full
 
 
 def all_shards(q_heads: int, kv_heads: int, world: int):

@@ -65,3 +65,38 @@ def test_gather_heads_two_ranks_gloo(hq, hkv, batch):
     for p in procs:
         p.join(60)
     assert res == [(0, True), (1, True)]
+
+
+def test_batch_shards_partition_the_sequences():
+    from pbs_attn_b200.sharding import shard_batch
+    for batch, world in [(8, 8), (8, 2), (5, 2), (3, 4), (1, 2)]:
+        parts = [shard_batch(batch, r, world) for r in range(world)]
+        assert [i for p in parts for i in range(p.start, p.stop)] == list(range(batch))
+        sizes = [p.stop - p.start for p in parts]
+        assert max(sizes) - min(sizes) <= 1
+
+
+def _batch_worker(rank, world, port, batch, q):
+    from pbs_attn_b200.sharding import gather_batch, shard_batch
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = torch.arange(batch * 2 * 6 * 4, dtype=torch.float32).view(batch, 2, 6, 4)
+        got = gather_batch(full[shard_batch(batch, rank, world)].clone(), batch)
+        q.put((rank, bool(torch.equal(got, full))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("batch", [4, 3, 1])
+def test_gather_batch_two_ranks_gloo(batch):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_batch_worker, args=(r, 2, port, batch, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert res == [(0, True), (1, True)]
