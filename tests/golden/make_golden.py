@@ -1,9 +1,9 @@
 """Generates tests/golden/*.npz by running the UNMODIFIED reference on seeded inputs.
 
-Run once, in a container that has the reference checked out (it is imported
-from REFERENCE_ROOT, default /root/reference, and is not needed afterwards):
+Run once, on a machine that has the reference checked out (it is imported from the
+directory named by the REFERENCE_ROOT environment variable and is not needed afterwards):
 
-    python tests/golden/make_golden.py [--meanpooling-only]
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [--meanpooling-only]
 
 Per case two runs are stored: ``*_ref`` from the reference as it is (its sorts
 are non-stable: the order of tied items is implementation defined) and
@@ -23,7 +23,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT")
+if not REFERENCE_ROOT:
+    raise SystemExit("set REFERENCE_ROOT to the directory of the reference checkout")
 
 
 def _import_reference():
