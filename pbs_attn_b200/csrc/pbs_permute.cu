@@ -45,7 +45,11 @@ segment_permute_kernel(const float* __restrict__ importance,
       keys[i] = key;
     }
     __syncthreads();
-    bitonic_sort_desc(keys, npow2);
+    // 256 threads: up to 4 keys per thread sort in registers and shuffles, larger segments in shared memory
+    if (npow2 <= 256) bitonic_sort_desc_regs<1>(keys, npow2);
+    else if (npow2 == 512) bitonic_sort_desc_regs<2>(keys, npow2);
+    else if (npow2 == 1024) bitonic_sort_desc_regs<4>(keys, npow2);
+    else bitonic_sort_desc(keys, npow2);
     for (int i = threadIdx.x; i < seg; i += blockDim.x)
       order[i] = seg0 + (int32_t)(0xFFFFFFFFu - (uint32_t)(keys[i] & 0xFFFFFFFFull));
   } else {
