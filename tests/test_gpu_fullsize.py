@@ -124,3 +124,19 @@ def test_sweep_shapes_tcgen05_agrees_with_generic_kernel(hq, hkv, d, s, dt, bs, 
     torch.cuda.synchronize()
     dd = (out.float() - ref.float()).abs()
     assert dd.max().item() <= 2e-2 and dd.mean().item() <= 2e-3, (dd.max().item(), dd.mean().item())
+
+
+def test_one_head_pair_at_524288_tokens():
+    """The longest context of the reference's efficiency sweep (512K, run there over 8 GPUs: this is a
+    2-query-head slice of one rank's share).  Index arithmetic at that size: structure invariants on the
+    sparse call, and the select-all call against dense causal attention."""
+    w = LLAMA8B_128K.with_(q_heads=2, kv_heads=1, seq_len=524288, name="llama8b_heads_s524288_h2")
+    q, k, v = make_qkv(w, seed=11, device="cuda")
+    out, inter = _run(w, q, k, v)
+    _structure_checks(w, inter)
+    assert torch.isfinite(out.float()).all()
+    del out, inter
+    dense_out, _ = _run(w, q, k, v, threshold=1, force_select_first_block=False)
+    dense = torch.nn.functional.scaled_dot_product_attention(q, k.expand(-1, 2, -1, -1), v.expand(-1, 2, -1, -1), is_causal=True)
+    d = (dense_out.float() - dense.float()).abs()
+    assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3, (d.max().item(), d.mean().item())
