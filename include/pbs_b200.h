@@ -148,6 +148,16 @@ int pbs_segment_permute(const pbs_shape_t* shape, const float* importance,
                         void* pooled_k, int32_t key_pool_mode, int32_t* first_block,
                         void* stream);
 
+/* Caller side of the path (the step before it).  Rotary position embedding applied IN PLACE to a
+ * (B, H, S, D) tensor of projected queries or keys: x <- x * cos + rotate_half(x) * sin, with each
+ * product and the sum rounded to the tensor's type exactly as the separate tensor operations of
+ * pbs_attn/patch/huggingface.py:14-26 (called at :203) round them.  cos and sin are (B or 1, S, D)
+ * tables of the same type; cs_strides = {batch stride (0 to broadcast), position stride, 1}.
+ * Each half row (head_dim / 2 elements) must be a whole number of 16-byte pieces. */
+int pbs_apply_rope(int32_t dtype, int32_t batch, int32_t heads, int32_t seq_len, int32_t head_dim,
+                   void* x, const int64_t x_strides[4], const void* cos_table, const void* sin_table,
+                   const int64_t cs_strides[3], void* stream);
+
 /* Stage 2a.  Block pooling of the queries.  Replaces pbs_attn/src/utils.py:18-21. */
 int pbs_pool_queries(const pbs_shape_t* shape, const void* q, const int64_t q_strides[4],
                      void* pooled_q, int32_t query_pool_mode, void* stream);

@@ -50,6 +50,7 @@ _ST = C.POINTER(C.c_int64)
 SIGNATURES = {
     "pbs_scratch_sizes": [_SH, C.POINTER(ScratchSizes)],
     "pbs_key_importance": [_SH, _P, _ST, _P, _ST, _P, _P, _P, _P, _P],
+    "pbs_apply_rope": [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _ST, _P, _P, _ST, _P],
     "pbs_key_importance_static": [_SH, _P, _ST, _P, _ST, _P, _P],
     "pbs_segment_permute": [_SH, _P, _P, _ST, _P, _ST, _P, _P, _P, _P, C.c_int32, _P, _P],
     "pbs_pool_queries": [_SH, _P, _ST, _P, C.c_int32, _P],

@@ -140,6 +140,28 @@ int pbs_pool_queries(const pbs_shape_t* shape, const void* q, const int64_t q_st
   return launch_pool_queries(make_dims(*shape), shape->dtype, q, qs, pooled_q, query_pool_mode, (cudaStream_t)stream);
 }
 
+int pbs_apply_rope(int32_t dtype, int32_t batch, int32_t heads, int32_t seq_len, int32_t head_dim,
+                   void* x, const int64_t x_strides[4], const void* cos_table, const void* sin_table,
+                   const int64_t cs_strides[3], void* stream) {
+  if (dtype < PBS_BF16 || dtype > PBS_FP32) { set_error("dtype %d is not bf16/fp16/fp32", dtype); return PBS_ERR_ARG; }
+  if (batch < 1 || heads < 1 || seq_len < 1) { set_error("batch, heads and seq_len must be positive"); return PBS_ERR_SHAPE; }
+  const int e = elem_bytes(dtype);
+  if (head_dim < 2 || head_dim % 2 || (head_dim / 2 * e) % 16) {
+    set_error("head_dim %d: half a row must be a whole number of 16-byte pieces", head_dim);
+    return PBS_ERR_SHAPE;
+  }
+  Strides xs;
+  PBS_TRY(check_tensor("x", x, x_strides, dtype, &xs));
+  PBS_NONNULL(cos_table); PBS_NONNULL(sin_table); PBS_NONNULL(cs_strides);
+  if (cs_strides[2] != 1 || cs_strides[0] < 0 || cs_strides[1] <= 0 || ((cs_strides[0] * e) & 15) || ((cs_strides[1] * e) & 15) ||
+      ((uintptr_t)cos_table & 15) || ((uintptr_t)sin_table & 15)) {
+    set_error("cos/sin tables: need unit innermost stride and 16-byte aligned rows");
+    return PBS_ERR_LAYOUT;
+  }
+  return launch_rope(dtype, batch, heads, seq_len, head_dim, x, xs, cos_table, sin_table, cs_strides[0], cs_strides[1],
+                     (cudaStream_t)stream);
+}
+
 int pbs_select_blocks(const pbs_shape_t* shape, const void* pooled_q, const void* pooled_k,
                       const int32_t* first_block, const pbs_options_t* options, uint8_t* block_mask,
                       float* block_scores, void* stream) {

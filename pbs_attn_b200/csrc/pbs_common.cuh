@@ -195,6 +195,8 @@ int launch_segment_permute(const Dims& d, int dt, const float* importance, const
                            void* pooled_k, int pool_mode, int32_t* first_block, cudaStream_t st);
 int launch_pool_queries(const Dims& d, int dt, const void* q, Strides qs, void* pooled_q, int pool_mode,
                         cudaStream_t st);
+int launch_rope(int dt, int B, int H, int S, int D, void* x, Strides xs, const void* cosp, const void* sinp,
+                int64_t cs_b, int64_t cs_s, cudaStream_t st);
 int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void* pooled_k,
                          const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, float* scores,
                          cudaStream_t st);

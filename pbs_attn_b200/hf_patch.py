@@ -74,6 +74,21 @@ def get_meanpooling_prefill(block_size=128, segment_size=1024, threshold=0.9,
                    force_select_current_block=force_select_current_block)
 
 
+def _fused_rope_applies(q, k, cos, sin) -> bool:
+    """The CUDA library's in-place rotary kernel replaces the five tensor operations of
+    ``apply_rotary_pos_emb`` when the tensors are on a GPU, share a supported dtype and nothing needs
+    gradients (the projections' outputs are fresh tensors, so writing in place is safe)."""
+    if not (q.is_cuda and k.is_cuda and cos.is_cuda) or torch.is_grad_enabled() and (q.requires_grad or k.requires_grad):
+        return False
+    if q.dtype not in (torch.bfloat16, torch.float16, torch.float32) or not (k.dtype == cos.dtype == sin.dtype == q.dtype):
+        return False
+    d = q.shape[-1]
+    if cos.dim() != 3 or cos.shape[-1] != d or cos.shape[-2] != q.shape[-2] or (d // 2 * q.element_size()) % 16 or d % 2:
+        return False
+    e = q.element_size()
+    return all(t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all((st * e) % 16 == 0 for st in t.stride()[:3]) for t in (q, k))
+
+
 def _kernel_of(prefill_fn):
     return prefill_fn.func if isinstance(prefill_fn, partial) else prefill_fn
 
@@ -118,7 +133,11 @@ def patched_attention_forward(
     k = k.view(bsz, q_len, n_kv, d).transpose(1, 2)
     v = v.view(bsz, q_len, n_kv, d).transpose(1, 2)
     cos, sin = position_embeddings
-    q, k = apply_rotary_pos_emb(q, k, cos, sin)
+    if _fused_rope_applies(q, k, cos, sin):
+        from .prefill import apply_rope_
+        q, k = apply_rope_(q, cos, sin), apply_rope_(k, cos, sin)     # one pass each, in place
+    else:
+        q, k = apply_rotary_pos_emb(q, k, cos, sin)
     if past_key_values is not None:
         past_key_values.update(k, v, self.layer_idx, {"sin": sin, "cos": cos, "cache_position": cache_position})
     if not _takes_grouped_kv(prefill_fn):

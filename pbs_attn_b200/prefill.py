@@ -183,6 +183,29 @@ _PLANS: dict = {}
 _MAX_PLANS = 2
 
 
+def apply_rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary position embedding of (B, H, S, D) queries or keys IN PLACE, in one pass on the CUDA
+    library: x <- x * cos + rotate_half(x) * sin with the roundings of the separate tensor operations
+    of pbs_attn/patch/huggingface.py:14-26.  cos / sin: (B or 1, S, D), same dtype as x."""
+    if not x.is_cuda:
+        raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
+    B, H, S, D = x.shape
+    if cos.dim() != 3 or cos.shape[-2:] != (S, D) or sin.shape != cos.shape or cos.dtype != x.dtype or sin.dtype != x.dtype:
+        raise ValueError("cos / sin must be (B or 1, S, D) tables of x's dtype")
+    if x.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {x.dtype}: need bfloat16, float16 or float32")
+    e = x.element_size()
+    if not all(t.stride(2) == 1 and t.data_ptr() % 16 == 0 and (t.stride(1) * e) % 16 == 0 and (t.stride(0) * e) % 16 == 0
+               for t in (cos, sin)) or sin.stride() != cos.stride():
+        cos, sin = cos.contiguous(), sin.contiguous()
+    cs = (C.c_int64 * 3)(cos.stride(0) if cos.shape[0] > 1 else 0, cos.stride(1), 1)
+    lib = _cabi.load()
+    with torch.cuda.device(x.device):
+        _cabi.check(lib.pbs_apply_rope(_DTYPES[x.dtype], B, H, S, D, _ptr(x), _strides(x), _ptr(cos), _ptr(sin), cs,
+                                       C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)), "pbs_apply_rope")
+    return x
+
+
 def get_plan(q: torch.Tensor, kv_heads: int, block_size: int, segment_size: int) -> Plan:
     """Scratch is reused between calls of the same shape on the same device (e.g. the layers
     of one model); at most two shapes stay cached."""
