@@ -66,8 +66,11 @@ def dense_equiv_flops(w: Workload, q_heads: int) -> float:
 
 
 class ClockSampler:
-    """nvidia-smi in the background while the timed region runs (read-only queries)."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi in the background (read-only queries).  It is started well before the timed region,
+    because it needs most of a second to deliver its first sample, and ``stop`` keeps the samples whose
+    time stamps fall inside the region: the clock UNDER LOAD (this GPU runs into its power cap, so the
+    loaded clock is the lower one)."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
@@ -79,12 +82,14 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.gpu)], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t0: float, t1: float):
+        """Summary of the samples taken between the host times ``t0`` and ``t1`` (time.time())."""
+        import datetime
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -93,26 +98,36 @@ class ClockSampler:
                 self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        sm, smax, reasons = [], 0.0, set()
+        sm, power, smax, reasons, total = [], [], 0.0, set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.file.read().splitlines():
             c = [x.strip() for x in line.split(",")]
             if len(c) < 8:
                 continue
             try:
-                sm.append(float(c[1]))
-                smax = max(smax, float(c[2]))
+                ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, cmax = float(c[1]), float(c[2])
             except ValueError:
                 continue
+            total += 1
+            smax = max(smax, cmax)
+            if not (t0 <= ts <= t1):
+                continue
+            sm.append(clk)
+            try:
+                power.append(float(c[3]))
+            except ValueError:
+                pass
             for n, v in zip(names, c[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         self.file.close()
         os.unlink(self.file.name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        busy = sorted(sm)[len(sm) // 4:]        # drop the idle quarter at the edges of the region
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": smax or None, "reasons": [], "samples": 0, "samples_total": total}
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": smax,
+                "power_w": statistics.median(power) if power else None, "reasons": sorted(reasons),
+                "samples": len(sm), "samples_total": total}
 
 
 def cpu_port_run(w: Workload, seed: int):
@@ -198,6 +213,9 @@ def run_ours(args, w: Workload):
         dist.init_process_group("nccl", device_id=dev)
     lib = _cabi.load()
     peaks = load_peaks()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
 
     sh = shard_heads(w.q_heads, w.kv_heads, rank, world)
     wl = w.with_(q_heads=sh.q_count, kv_heads=sh.kv_count)
@@ -223,17 +241,16 @@ def run_ours(args, w: Workload):
     plan.check_status()
     n_sel_local = float(plan.block_mask.sum().item())
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = lib.pbs_launch_count()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     barrier()
+    t_timed0 = time.time()
     ev[0].record()
     for _ in range(args.steps):
         out = step()
     ev[1].record()
     barrier()
+    t_timed1 = time.time()
     launches = lib.pbs_launch_count() - launches0
     ms_total = ev[0].elapsed_time(ev[1])
     plan.check_status()
@@ -257,7 +274,7 @@ def run_ours(args, w: Workload):
     ev2[1].record()
     barrier()
     e2e_ms_total = ev2[0].elapsed_time(ev2[1])
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_timed0, t_timed1) if rank == 0 else None
 
     # ---- per-stage device times on this rank (the attention kernel gives the roofline)
     opt = plan.options(w.threshold)
