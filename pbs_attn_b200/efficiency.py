@@ -10,6 +10,13 @@ latencies are comparable, selection densities are whatever random weights give a
 
     python -m pbs_attn_b200.efficiency --method pbs --lens 8192,32768,131072
     python -m pbs_attn_b200.efficiency --method dense --layers 8
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m pbs_attn_b200.efficiency --lens 262144
+
+Under ``torch.distributed.run`` the model is tensor-parallel the way the reference's script runs it
+(``tp_plan="auto"``, eval_efficiency.py:197-203, scripts/eval_efficiency.sh:14-22: 256K tokens on 4 GPUs, 512K on
+8): every rank holds its slice of the attention heads and of the MLP width, and the outputs of ``o_proj`` and
+``down_proj`` are summed over the ranks (one NCCL all-reduce each).  Random weights need no loading, so each rank
+simply builds the architecture with its share of the heads; the attention kernels see exactly a rank's heads.
 
 Prints one JSON line per context length.
 """
@@ -29,13 +36,46 @@ ARCHS = {
 }
 
 
-def build_model(arch: str, layers=None, device="cuda", seed=0):
-    """Random-init bf16 model of the named architecture, built directly on the device."""
+def shard_config(kw: dict, world: int) -> dict:
+    """The architecture one tensor-parallel rank holds: heads, KV heads and MLP width divided by ``world``;
+    hidden size, vocabulary and layer count unchanged (column-parallel q/k/v/gate/up, row-parallel o/down)."""
+    if world == 1:
+        return kw
+    kw = dict(kw)
+    if kw["num_attention_heads"] % world or kw["num_key_value_heads"] % world or kw["intermediate_size"] % world:
+        raise ValueError(f"{world} ranks do not divide the heads / MLP width of this architecture")
+    kw.setdefault("head_dim", kw["hidden_size"] // kw["num_attention_heads"])
+    kw["num_attention_heads"] //= world
+    kw["num_key_value_heads"] //= world
+    kw["intermediate_size"] //= world
+    return kw
+
+
+def add_row_parallel_reductions(model, group=None):
+    """Sums the outputs of every ``o_proj`` and ``down_proj`` over the ranks, which is what makes the
+    per-rank slices of ``shard_config`` one tensor-parallel model."""
+    import torch.distributed as dist
+
+    def hook(_module, _inputs, output):
+        dist.all_reduce(output, group=group)
+        return output
+
+    handles = []
+    for layer in model.model.layers:
+        handles.append(layer.self_attn.o_proj.register_forward_hook(hook))
+        handles.append(layer.mlp.down_proj.register_forward_hook(hook))
+    return handles
+
+
+def build_model(arch: str, layers=None, device="cuda", seed=0, world=1):
+    """Random-init bf16 model of the named architecture (one rank's share of it when ``world`` > 1),
+    built directly on the device."""
     from transformers import LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM
     kw = dict(ARCHS[arch])
     kind = kw.pop("kind")
     if layers:
         kw["num_hidden_layers"] = layers
+    kw = shard_config(kw, world)
     cfg = (LlamaConfig if kind == "llama" else Qwen2Config)(**kw)
     torch.manual_seed(seed)
     prev = torch.get_default_dtype()
@@ -108,19 +148,35 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("the efficiency harness needs a CUDA device")
+    import os
+    import torch.distributed as dist
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from .hf_patch import apply_patch_with_prefill
-    model = build_model(args.arch, args.layers)
+    model = build_model(args.arch, args.layers, device=f"cuda:{local_rank}", world=world)
+    if world > 1:
+        add_row_parallel_reductions(model)
     if args.method != "unpatched":
         apply_patch_with_prefill(model, prefill_function(args.method, args.block_size, args.segment_size, args.threshold))
     model.generation_config.pad_token_id = 0
     vocab = model.get_input_embeddings().weight.size(0)
-    gen = torch.Generator(device="cuda").manual_seed(0)
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=dev).manual_seed(0)            # same ids on every rank
     for length in [int(x) for x in args.lens.split(",")]:
-        ids = torch.randint(0, vocab, (1, length), device="cuda", dtype=torch.long, generator=gen)
+        ids = torch.randint(0, vocab, (1, length), device=dev, dtype=torch.long, generator=gen)
         for _ in range(args.warmup):
             measure_prefill_latency(model, ids)
         times = [measure_prefill_latency(model, ids) for _ in range(args.iters)]
-        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers,
+        if world > 1:                                            # a step ends when the slowest rank ends
+            t = torch.tensor(times, dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times = t.tolist()
+        if rank != 0:
+            continue
+        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers, "tp": world,
                "method": args.method, "len": length, "mean_s": sum(times) / len(times), "min_s": min(times),
                "iters": args.iters, "warmup": args.warmup, "weights": "random-init", "prompts": "uniform random ids",
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
@@ -128,6 +184,8 @@ def main(argv=None):
             rec.update(block_size=args.block_size, segment_size=args.segment_size, threshold=args.threshold,
                        last_layer_density=last_density())
         print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

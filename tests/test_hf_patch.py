@@ -101,3 +101,59 @@ def test_patched_model_on_gpu_select_all_equals_dense(kind):
         sparse = model(ids).logits.float()
         out = model.generate(ids[:, :300], max_new_tokens=3, do_sample=False)
     assert torch.isfinite(sparse).all() and out.shape[1] == 303
+
+
+def test_shard_config_divides_heads_and_mlp_width():
+    from pbs_attn_b200.efficiency import ARCHS, shard_config
+    kw = {k: v for k, v in ARCHS["llama3.1-8b"].items() if k != "kind"}
+    s = shard_config(kw, 4)
+    assert (s["num_attention_heads"], s["num_key_value_heads"], s["intermediate_size"]) == (8, 2, 14336 // 4)
+    assert s["hidden_size"] == kw["hidden_size"] and s["head_dim"] == 128
+    q = {k: v for k, v in ARCHS["qwen2.5-7b"].items() if k != "kind"}
+    assert shard_config(q, 4)["head_dim"] == 128 and shard_config(q, 4)["num_key_value_heads"] == 1
+    with pytest.raises(ValueError):
+        shard_config(q, 8)                       # 4 KV heads do not split over 8 ranks
+    assert shard_config(kw, 1) is kw
+
+
+def _tp_worker(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    from pbs_attn_b200 import efficiency
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        efficiency.ARCHS["tiny"] = dict(kind="llama", vocab_size=128, hidden_size=64, intermediate_size=128,
+                                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                        max_position_embeddings=256)
+        model = efficiency.build_model("tiny", device="cpu", world=world).float()
+        efficiency.add_row_parallel_reductions(model)
+        apply_patch_with_prefill(model, dense_prefill)
+        ids = torch.arange(24).view(1, 24) % 128
+        with torch.no_grad():
+            logits = model(ids).logits
+        gathered = [torch.empty_like(logits) for _ in range(world)]
+        dist.all_gather(gathered, logits)
+        heads = model.model.layers[0].self_attn.q_proj.out_features // 16
+        q.put((rank, heads, bool(torch.equal(gathered[0], gathered[1])), bool(torch.isfinite(logits).all())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_slices_run_and_agree_two_ranks_gloo():
+    """Two CPU ranks, each holding half of the heads and of the MLP width, with the row-parallel sums in
+    place: both must produce the same (finite) logits through the patched attention forward."""
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert res == [(0, 2, True, True), (1, 2, True, True)]
