@@ -77,6 +77,15 @@ def build_model(arch: str, layers=None, device="cuda", seed=0, world=1):
         kw["num_hidden_layers"] = layers
     kw = shard_config(kw, world)
     cfg = (LlamaConfig if kind == "llama" else Qwen2Config)(**kw)
+    if str(device).startswith("cuda"):
+        # With the default attention setting the model materialises a (S, S) boolean causal mask for
+        # every call (64 GiB at 262144 tokens); the flash-attention setting passes no dense mask.  The
+        # patched layers never look at the mask, and single-token decode runs the library kernel.
+        try:
+            import flash_attn  # noqa: F401
+            cfg._attn_implementation = "flash_attention_2"
+        except ImportError:
+            pass
     torch.manual_seed(seed)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
@@ -145,6 +154,9 @@ def main(argv=None):
     ap.add_argument("--threshold", type=float, default=0.9)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--slice-of", type=int, default=1, metavar="N",
+                    help="on ONE GPU, run the slice one rank of an N-way tensor-parallel model holds, without the "
+                         "all-reduces: the compute side of a multi-GPU point when no multi-GPU machine is at hand")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("the efficiency harness needs a CUDA device")
@@ -156,7 +168,9 @@ def main(argv=None):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     from .hf_patch import apply_patch_with_prefill
-    model = build_model(args.arch, args.layers, device=f"cuda:{local_rank}", world=world)
+    if args.slice_of > 1 and world > 1:
+        raise SystemExit("--slice-of is for single-process runs")
+    model = build_model(args.arch, args.layers, device=f"cuda:{local_rank}", world=max(world, args.slice_of))
     if world > 1:
         add_row_parallel_reductions(model)
     if args.method != "unpatched":
@@ -176,7 +190,7 @@ def main(argv=None):
             times = t.tolist()
         if rank != 0:
             continue
-        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers, "tp": world,
+        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers, "tp": world, "slice_of": args.slice_of,
                "method": args.method, "len": length, "mean_s": sum(times) / len(times), "min_s": min(times),
                "iters": args.iters, "warmup": args.warmup, "weights": "random-init", "prompts": "uniform random ids",
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
