@@ -384,6 +384,9 @@ def main():
     ap.add_argument("--workload", default="llama8b_heads_s131072", choices=sorted(WORKLOADS))
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--threshold", type=float, default=None)
+    ap.add_argument("--block-size", type=int, default=None, help="selection block size (64 or 128)")
+    ap.add_argument("--segment-size", type=int, default=None, help="permutation segment size")
+    ap.add_argument("--density", type=float, default=None, help="fraction of key positions planted as heavy hitters")
     ap.add_argument("--heads", default=None, metavar="HQ,HKV",
                     help="run a slice of the workload with this many query / KV heads (for profiler-sized cases)")
     ap.add_argument("--seed", type=int, default=0)
@@ -394,6 +397,12 @@ def main():
         w = w.with_(seq_len=args.seq_len, name=f"{w.name.rsplit('_s', 1)[0]}_s{args.seq_len}")
     if args.threshold is not None:
         w = w.with_(threshold=args.threshold)
+    if args.block_size:
+        w = w.with_(block_size=args.block_size, name=f"{w.name}_bs{args.block_size}")
+    if args.segment_size:
+        w = w.with_(segment_size=args.segment_size, name=f"{w.name}_seg{args.segment_size}")
+    if args.density is not None:
+        w = w.with_(density=args.density)
     if args.heads:
         hq, hkv = (int(x) for x in args.heads.split(","))
         w = w.with_(q_heads=hq, kv_heads=hkv, name=f"{w.name}_h{hq}x{hkv}")

@@ -116,12 +116,17 @@ class Plan:
             raise _cabi.PbsError(f"device-side error flags {st.tolist()}: a bounded wait in the attention kernel ran out")
 
     # ------------------------------------------------------------------ stages
-    def key_importance(self, q, k):
+    def key_importance(self, q, k, want_logits: bool = False):
+        """Returns the (B, Hq, L) importance; with ``want_logits`` also the (B, Hq, block_size, L)
+        rounded scoring logits (for inspection and tests)."""
         _cabi.check(self.lib.pbs_key_importance(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
                                                 _ptr(self.logits), _ptr(self.partials), _ptr(self.rowstats),
                                                 _ptr(self.importance), self._stream()), "pbs_key_importance")
-        return self.importance[: self.shape.batch * self.shape.q_heads * self.n_complete].view(
-            self.shape.batch, self.shape.q_heads, self.n_complete)
+        B, H, L = self.shape.batch, self.shape.q_heads, self.n_complete
+        imp = self.importance[: B * H * L].view(B, H, L)
+        if want_logits:
+            return imp, self.logits[: B * H * self.shape.block_size * L].view(B, H, self.shape.block_size, L)
+        return imp
 
     def segment_permute(self, k, v, key_pool_mode="mean", identity=False):
         imp = None if identity else _ptr(self.importance)

@@ -104,3 +104,80 @@ def classify_mask(mask_got, mask_want, scores, threshold, blocks_per_segment, at
         if not (tie or boundary):
             bad += 1
     return n_rows, bad
+
+
+def classify_permutation_chain(idx_got, idx_want, imp_got, imp_want, segment_size, rel=2e-5):
+    """Exact accounting of permutation differences for 16-bit inputs.
+
+    ``imp_got`` is the importance the CUDA path sorted (its own fp32 output), ``imp_want`` the
+    oracle's.  Two links are checked:
+      1. ``idx_got`` is EXACTLY the stable descending per-segment sort of ``imp_got`` (the sort
+         itself has no tolerance);
+      2. where ``idx_got`` and ``idx_want`` differ, the keys whose importance differs between the
+         two runs beyond ``rel`` (the keys hit by a one-step flip of a scoring logit: the GEMM
+         summation order is not part of the reference's contract) are set aside per segment; the
+         remaining keys must appear in the same relative order in both permutations, except
+         neighbours whose oracle importance is within ``rel`` (fp32 near-ties).  A segment where
+         that fails is *unexplained*.
+    Returns a dict of counts.
+    """
+    idx_got, idx_want = idx_got.long(), idx_want.long()
+    B, H, S = idx_want.shape
+    L = imp_want.shape[-1]
+    nseg = L // segment_size
+    own = torch.argsort(imp_got.view(B, H, nseg, segment_size), dim=-1, descending=True, stable=True)
+    own = (own + torch.arange(0, L, segment_size).view(1, 1, nseg, 1)).reshape(B, H, L)
+    sort_exact = bool(torch.equal(own, idx_got[..., :L])) and bool(torch.equal(idx_got[..., L:], idx_want[..., L:]))
+    diff = idx_got[..., :L] != idx_want[..., :L]
+    n_diff = int(diff.sum())
+    seg_diff = diff.view(B, H, nseg, segment_size).any(-1)
+    moved = (imp_got - imp_want).abs() > rel * torch.maximum(imp_got.abs(), imp_want.abs())
+    n_unexplained = 0
+    n_affected = 0
+    for b, h, s in torch.nonzero(seg_diff).tolist():
+        lo = s * segment_size
+        g = idx_got[b, h, lo:lo + segment_size]
+        w = idx_want[b, h, lo:lo + segment_size]
+        hit = moved[b, h]
+        n_affected += int(hit[lo:lo + segment_size].sum())
+        g2, w2 = g[~hit[g]], w[~hit[w]]
+        bad = g2 != w2
+        if bool(bad.any()):
+            a, c = imp_want[b, h][g2[bad]], imp_want[b, h][w2[bad]]
+            if not bool(((a - c).abs() <= rel * torch.maximum(a.abs(), c.abs())).all()):
+                n_unexplained += 1
+    return {"idx_sort_exact": sort_exact, "idx_diff_slots": n_diff, "idx_slots": int(idx_want.numel()),
+            "idx_diff_segments": int(seg_diff.sum()), "idx_keys_with_moved_importance": n_affected,
+            "idx_unexplained_segments": n_unexplained}
+
+
+def attended_key_signature(idx, mask, block_size):
+    """(B, H, nb) int64: an order-independent signature of the SET of keys each q block attends (sum
+    over its selected kv blocks of a per-block hash of the original positions the block holds).
+    Equal signatures of two runs mean the two q blocks attend the same keys even when permutation
+    or mask differ in ways that cancel (e.g. two keys swapped between two selected blocks)."""
+    B, H, S = idx.shape
+    nb = mask.shape[-1]
+    pad = nb * block_size - S
+    x = idx.long()
+    if pad:
+        x = torch.cat([x, torch.full((B, H, pad), -1, dtype=torch.long)], dim=-1)
+    hsh = ((x + 7) * 2654435761 % 2147483647) * (x >= 0)
+    per_block = hsh.view(B, H, nb, block_size).sum(-1)                    # (B, H, nb)
+    return (mask.long() * per_block[:, :, None, :]).sum(-1)
+
+
+def parity_report(request, **fields):
+    """One machine-readable line per parity case: printed, attached to the junit record, and appended
+    to the file named by PBS_PARITY_REPORT when that is set."""
+    import json
+    rec = {"test": request.node.name}
+    rec.update(fields)
+    line = json.dumps(rec, sort_keys=True)
+    print("PARITY " + line)
+    for k, v in fields.items():
+        request.node.user_properties.append((k, v))
+    path = os.environ.get("PBS_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(line + "\n")
