@@ -6,8 +6,10 @@
 One step = one permuted_block_sparse_attn_fwd call (all stages) on the Llama-3.1-8B head shape at
 131072 tokens (32 query / 8 KV heads, head_dim 128, bf16, block 128, segment 256, threshold 0.9,
 seeded synthetic Q/K/V with planted heavy-hitter keys, sinks and RoPE).  With N > 1 the KV-head
-groups are sharded over the ranks (strong scaling: the total work is fixed) and the step ends with
-the NCCL all-gather of the outputs.  Rank 0 prints one JSON line.
+groups are sharded over the ranks (strong scaling: the total work is fixed, and every N works on the
+same seeded problem) and the step delivers the full (B, Hq, S, D) result to every rank: by default the
+attention kernel stores each output tile into every rank's buffer over NVLink (--gather fused), else an
+NCCL all-gather follows the call (--gather nccl).  Rank 0 prints one JSON line.
 
   value      selected-block TFLOP/s (4 * bs^2 * D per selected block) of the whole job, inputs
              resident in HBM, device time by CUDA events, max over ranks
@@ -36,11 +38,14 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-from pbs_attn_b200.synth import WORKLOADS, Workload, make_qkv  # noqa: E402
+from pbs_attn_b200.synth import WORKLOADS, Workload, make_qkv, make_qkv_heads  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch on one GPU, from the ncu
-# captures summarised under profiles/ (bytes); other workloads have no capture.
-ATTN_KERNEL_DRAM_TRAFFIC = {"llama8b_heads_s131072": 20.20e9}
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_tc_kernel launch on one GPU (bytes), from the ncu
+# capture summarised in the named file under profiles/, with the commit whose kernel was captured: a later
+# change of the kernel makes the figure stale until the capture is repeated.  Other workloads have none.
+ATTN_KERNEL_DRAM_TRAFFIC = {
+    "llama8b_heads_s131072": {"bytes": 20.20e9, "commit": "8ed0ae1", "profile": "profiles/attn_tc_kernel_llama8b_s32768.txt"},
+}
 
 METRIC = "prefill_attn_selected_block_tflops"
 UNIT = "TFLOP/s"
@@ -186,7 +191,11 @@ def run_reference(args, w: Workload):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": config_dict(w, 1, {"measured_on": "bounded sample, see cpu_baseline.sample"}),
+        "config": config_dict(w, 1, {"measured_on": "bounded sample, see sample_config"}),
+        "same_config": False,
+        "sample_config": {"q_heads": ws.q_heads, "kv_heads": ws.kv_heads, "seq_len": ws.seq_len, "batch": ws.batch,
+                          "note": "the CPU port of the reference path (oracle/) is timed on one KV group at this length; "
+                                  "value is a RATE (selected-block TFLOP/s), not the time of the full configuration"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample_text(ws)},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -199,7 +208,7 @@ def run_reference(args, w: Workload):
 def run_ours(args, w: Workload):
     import torch.distributed as dist
     from pbs_attn_b200 import _cabi
-    from pbs_attn_b200.prefill import get_plan, permuted_block_sparse_attn_fwd
+    from pbs_attn_b200.prefill import get_plan, permuted_block_sparse_attn_fwd, permuted_block_sparse_attn_fwd_host
     from pbs_attn_b200.sharding import gather_heads, shard_heads
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -217,12 +226,25 @@ def run_ours(args, w: Workload):
     if rank == 0:
         sampler.start()
 
+    # Every partition of the heads works on the same global problem: inputs are drawn per KV-head group.
     sh = shard_heads(w.q_heads, w.kv_heads, rank, world)
-    wl = w.with_(q_heads=sh.q_count, kv_heads=sh.kv_count)
-    q, k, v = make_qkv(wl, args.seed + rank, device=dev)
+    q, k, v = make_qkv_heads(w, args.seed, sh.kv_start, sh.kv_count, sh.q_start, sh.q_count, device=dev)
     torch.cuda.synchronize()
 
+    # ---- how the full (B, Hq, S, D) result reaches every rank
+    gather_mode, gather_note, fused = "none", None, None
+    if world > 1:
+        gather_mode = args.gather
+        if gather_mode == "fused":
+            try:
+                from pbs_attn_b200.peer_gather import FusedHeadGather, permuted_block_sparse_attn_fwd_gathered
+                fused = FusedHeadGather(w.batch, w.q_heads, w.kv_heads, w.seq_len, w.head_dim, q.dtype, dev)
+            except Exception as e:      # e.g. CUDA IPC not permitted on this host: the NCCL all-gather still works
+                gather_mode, gather_note = "nccl", f"fused gather unavailable: {e}"
+
     def step():
+        if fused is not None:
+            return permuted_block_sparse_attn_fwd_gathered(fused, q, k, v, w.block_size, w.segment_size, w.threshold)
         out = permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, True)
         if world > 1:
             out = gather_heads(out, w.q_heads, w.kv_heads)
@@ -255,8 +277,29 @@ def run_ours(args, w: Workload):
     ms_total = ev[0].elapsed_time(ev[1])
     plan.check_status()
 
+    # ---- N > 1, outside the timed region: is the gathered tensor right?
+    gather_check = None
+    if world > 1:
+        local = permuted_block_sparse_attn_fwd(q, k, v, w.block_size, w.segment_size, w.threshold, True)
+        torch.cuda.synchronize()
+        own_equal = bool(torch.equal(out[:, sh.q_slice], local))
+        # a head this rank does not own, recomputed here from regenerated inputs: the next rank's first head
+        other = shard_heads(w.q_heads, w.kv_heads, (rank + 1) % world, world)
+        fq, fk, fv = make_qkv_heads(w, args.seed, other.kv_start, 1, other.q_start, 1, device=dev)
+        foreign = permuted_block_sparse_attn_fwd(fq, fk, fv, w.block_size, w.segment_size, w.threshold, True)
+        torch.cuda.synchronize()
+        fd = (out[:, other.q_start:other.q_start + 1].float() - foreign.float()).abs().max().item()
+        ok = torch.tensor([int(own_equal), int(fd <= 2e-2)], dtype=torch.int32, device=dev)
+        fmax = torch.tensor([fd], dtype=torch.float64, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        dist.all_reduce(fmax, op=dist.ReduceOp.MAX)
+        gather_check = {"own_slice_bit_equal_on_all_ranks": bool(ok[0].item()),
+                        "foreign_head_recomputed_max_abs_over_ranks": float(fmax.item()),
+                        "foreign_head_within_tolerance_on_all_ranks": bool(ok[1].item())}
+        del local, foreign, fq, fk, fv
+        plan = get_plan(q, sh.kv_count, w.block_size, w.segment_size)
+
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
-    from pbs_attn_b200.prefill import permuted_block_sparse_attn_fwd_host
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     ho = torch.empty(w.batch, sh.q_count, w.seq_len, w.head_dim, dtype=q.dtype).pin_memory()
 
@@ -266,7 +309,7 @@ def run_ours(args, w: Workload):
 
     e2e_step()
     barrier()
-    e2e_steps = max(1, min(args.steps, 3))
+    e2e_steps = max(1, args.steps)
     ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev2[0].record()
     for _ in range(e2e_steps):
@@ -277,6 +320,7 @@ def run_ours(args, w: Workload):
     clocks = sampler.stop(t_timed0, t_timed1) if rank == 0 else None
 
     # ---- per-stage device times on this rank (the attention kernel gives the roofline)
+    plan = get_plan(q, sh.kv_count, w.block_size, w.segment_size)
     opt = plan.options(w.threshold)
     o2 = torch.empty_like(q)
     stage_calls = [
@@ -320,17 +364,15 @@ def run_ours(args, w: Workload):
         e2e_ms = e2e_ms_total / e2e_steps
         e2e_val = fl_sel / (e2e_ms * 1e-3) / 1e12
         esz = q.element_size()
-        h2d = (q.numel() + k.numel() + v.numel()) * esz
-        d2h = ho.numel() * esz
+        h2d = w.batch * (w.q_heads + 2 * w.kv_heads * max(1, world // w.kv_heads)) * w.seq_len * w.head_dim * esz
+        d2h = w.batch * w.q_heads * w.seq_len * w.head_dim * esz
         # attention kernel of THIS rank: its own selected blocks over its own duration
         attn_s = stage_ms["attention"] * 1e-3
         achieved = selected_flops(n_sel_local, w) / attn_s / 1e12
-        long_step = stage_ms["attention"] > 50.0
-        peak = peaks["bf16_sustained"] if long_step else peaks["bf16_burst"]
         B, Hq, Hkv, S, D, bs = w.batch, sh.q_count, sh.kv_count, w.seq_len, w.head_dim, w.block_size
         L = (S // w.segment_size) * w.segment_size
         stage_bytes = {      # algorithmic HBM bytes per launch group (this rank's heads)
-            "key_importance": B * Hkv * L * D * esz + B * Hq * bs * D * esz + 2 * B * Hq * bs * L * esz + 4 * B * Hq * L,
+            "key_importance": B * Hkv * L * D * esz + B * Hq * bs * D * esz + 4 * B * Hq * L,
             "segment_permute": 2 * B * Hkv * S * D * esz + 4 * B * Hq * L + 2 * B * Hq * S * D * esz + 4 * B * Hq * S + B * Hq * nb * D * esz,
             "pool_queries": B * Hq * S * D * esz + B * Hq * nb * D * esz,
             "select_blocks": 2 * B * Hq * nb * D * esz + B * Hq * nb * nb,
@@ -340,27 +382,35 @@ def run_ours(args, w: Workload):
         for n, by in stage_bytes.items():
             stages[n]["gbs"] = round(by / (stage_ms[n] * 1e-3) / 1e9, 1)
             stages[n]["frac_hbm"] = round(stages[n]["gbs"] / peaks["hbm_gbs"], 4)
+        traffic = ATTN_KERNEL_DRAM_TRAFFIC.get(w.name) if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-            "config": config_dict(w, world),
-            "density": n_sel / causal_blocks,
+            "config": config_dict(w, world, {"gather": gather_mode}),
             "selected_tflop_per_step": fl_sel / 1e12, "dense_equiv_tflop_per_step": fl_dense / 1e12,
             "dense_equiv_tflops": fl_dense / (ms_step * 1e-3) / 1e12,
-            "frac_bf16_peak": value / world / peak,
-            "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
+            "frac_bf16_burst_peak_whole_call_per_gpu": value / world / peaks["bf16_burst"],
+            "e2e": {"value": e2e_val, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": int(launches),
-            "roofline": {"kernel": "attn_tc_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": ATTN_KERNEL_DRAM_TRAFFIC.get(w.name) if world == 1 else None,
-                         "traffic_unit": "bytes per launch (ncu, see profiles/)",
-                         "peak_source": f"{peaks['source']} ({'sustained' if long_step else 'burst'})",
-                         "kernel_ms": stage_ms["attention"], "kernel_ms_max_over_ranks": attn_ms_max},
-            "stages": stages,
+            # frac is ALWAYS against the sustained measured peak (the kernel is timed back to back, at N = 1 it
+            # runs at the power cap); frac_burst is the same figure against the burst peak
+            "roofline": {"kernel": "attn_tc_kernel", "bound": "tensor", "achieved": achieved,
+                         "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
+                         "frac_sustained": achieved / peaks["bf16_sustained"], "frac_burst": achieved / peaks["bf16_burst"],
+                         "peak_burst": peaks["bf16_burst"], "peak_source": f"{peaks['source']} (sustained)",
+                         "traffic": traffic["bytes"] if traffic else None,
+                         "traffic_source": (f"ncu, {traffic['profile']}, kernel as of commit {traffic['commit']}" if traffic else None),
+                         "traffic_unit": "bytes per launch",
+                         "kernel_ms": stage_ms["attention"], "kernel_ms_max_over_ranks": attn_ms_max,
+                         "density": n_sel / causal_blocks, "stages": stages},
             "clocks": clocks,
         }
+        if gather_check is not None:
+            line["gather_check"] = gather_check
+        if gather_note:
+            line["gather_note"] = gather_note
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             ws = sample_workload(w)
@@ -372,6 +422,8 @@ def run_ours(args, w: Workload):
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
+        if fused is not None:
+            fused.close()
         dist.destroy_process_group()
 
 
@@ -390,6 +442,9 @@ def main():
     ap.add_argument("--heads", default=None, metavar="HQ,HKV",
                     help="run a slice of the workload with this many query / KV heads (for profiler-sized cases)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: outputs stored into every rank's full tensor by the attention kernel over NVLink "
+                         "(fused, the default), or an NCCL all-gather after the call")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]

@@ -196,7 +196,7 @@ def block_selection(q, perm_k, idx, block_size, segment_size, threshold,
 
 
 # --------------------------------------------------------------------------- stage 3
-def sparse_attention(q, perm_k, perm_v, idx, block_mask, block_size):
+def sparse_attention(q, perm_k, perm_v, idx, block_mask, block_size, empty_rows_zero=False):
     """Attention of every q block over its selected permuted kv blocks.
 
     pbs_attn/src/kernels/permuted_block_sparse_attention.py:314-384: logits / sqrt(D)
@@ -222,7 +222,10 @@ def sparse_attention(q, perm_k, perm_v, idx, block_mask, block_size):
                 s = torch.matmul(q[b, h, r0:r1], kk[cols].transpose(0, 1)) / math.sqrt(D)
                 visible = torch.arange(r0, r1)[:, None] >= pos[cols][None, :]
                 s = s.masked_fill(~visible, float("-inf"))
-                p = torch.softmax(s, dim=-1, dtype=torch.float32).to(q.dtype)
+                p = torch.softmax(s, dim=-1, dtype=torch.float32)
+                if empty_rows_zero:              # a row whose selected blocks hold no visible key attends nothing
+                    p = torch.nan_to_num(p, nan=0.0)
+                p = p.to(q.dtype)
                 out[b, h, r0:r1] = torch.matmul(p, vv[cols])
     return out
 
@@ -271,20 +274,23 @@ def meanpooling_block_mask(q, k, block_size, threshold, force_select_first_block
 
 
 def meanpooling_prefill(q, k, v, block_size=128, threshold=0.9, force_select_first_block=True,
-                        stable=True) -> OracleResult:
-    """pbs_attn/baselines/MeanPooling.py:7-111 with ``causal=True`` and the diagonal block forced.
+                        force_select_current_block=True, stable=True) -> OracleResult:
+    """pbs_attn/baselines/MeanPooling.py:7-111 with ``causal=True``.
 
     The reference hands its block mask to an external block-sparse flash-attention
     library with ``is_causal=True`` (MeanPooling.py:92-106): every selected block is
     attended, element-causally on the diagonal.  That library is not part of the
     reference project, so the attention itself is restated from its contract:
     softmax over the selected blocks' visible keys, the same arithmetic as
-    ``sparse_attention`` with the identity permutation.
+    ``sparse_attention`` with the identity permutation.  Without the forced diagonal block a query
+    row may have no visible key among its selected blocks (or no selected block at all); block-sparse
+    flash-attention kernels return zeros for such rows, and so does this restatement.
     """
     B, Hq, S, D = q.shape
     n_rep = Hq // k.shape[1]
     k, v = repeat_kv(k, n_rep), repeat_kv(v, n_rep)        # the baseline asserts Hq == Hkv (MeanPooling.py:21)
-    mask, scores = meanpooling_block_mask(q, k, block_size, threshold, force_select_first_block, True, stable)
+    mask, scores = meanpooling_block_mask(q, k, block_size, threshold, force_select_first_block,
+                                          force_select_current_block, stable)
     idx = torch.arange(S).view(1, 1, S).expand(B, Hq, S)
-    out = sparse_attention(q, k, v, idx, mask, block_size)
+    out = sparse_attention(q, k, v, idx, mask, block_size, empty_rows_zero=True)
     return OracleResult(out, idx, mask, scores, None)

@@ -34,11 +34,19 @@ class Scratch(C.Structure):
                  "pooled_q", "pooled_k", "first_block", "block_mask", "tile_list", "tile_count", "status")]
 
 
+MAX_OUT_REPLICAS = 15
+
+
+class OutReplicas(C.Structure):
+    _fields_ = [("count", C.c_int32), ("reserved", C.c_int32), ("out", C.c_void_p * MAX_OUT_REPLICAS)]
+
+
 class Options(C.Structure):
     _fields_ = [("threshold_per_head", C.c_void_p), ("threshold", C.c_float), ("select_all", C.c_int32),
                 ("force_select_first_block", C.c_int32), ("query_pool_mode", C.c_int32),
                 ("key_pool_mode", C.c_int32), ("attn_impl", C.c_int32), ("no_permutation", C.c_int32),
-                ("diagonal_candidates", C.c_int32)]
+                ("diagonal_candidates", C.c_int32), ("no_own_segment", C.c_int32),
+                ("out_replicas", C.POINTER(OutReplicas))]
 
 
 Strides4 = C.c_int64 * 4
@@ -48,6 +56,7 @@ _ST = C.POINTER(C.c_int64)
 
 # name -> argument types; every function returns int except the two noted below
 SIGNATURES = {
+    "pbs_debug_set_attn_wait": [C.c_int64, C.c_int32],
     "pbs_scratch_sizes": [_SH, C.POINTER(ScratchSizes)],
     "pbs_key_importance": [_SH, _P, _ST, _P, _ST, _P, _P, _P, _P, _P],
     "pbs_apply_rope": [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _ST, _P, _P, _ST, _P],
@@ -56,7 +65,12 @@ SIGNATURES = {
     "pbs_pool_queries": [_SH, _P, _ST, _P, C.c_int32, _P],
     "pbs_select_blocks": [_SH, _P, _P, _P, C.POINTER(Options), _P, _P, _P],
     "pbs_build_tile_lists": [_SH, _P, _P, _P, _P],
-    "pbs_attn_fwd": [_SH, _P, _ST, _P, _P, _P, _P, _P, _P, _P, _ST, C.c_int32, _P, _P],
+    "pbs_attn_fwd": [_SH, _P, _ST, _P, _P, _P, _P, _P, _P, _P, _ST, C.c_int32, _P, C.POINTER(OutReplicas), _P],
+    "pbs_debug_set_select_impl": [C.c_int32],
+    "pbs_enable_peer_access": [C.c_int32],
+    "pbs_ipc_export": [_P, C.POINTER(C.c_ubyte * 64), C.POINTER(C.c_int64)],
+    "pbs_ipc_import": [C.POINTER(C.c_ubyte * 64), C.POINTER(C.c_void_p)],
+    "pbs_ipc_release": [_P],
     "pbs_prefill_fwd": [_SH, _P, _ST, _P, _ST, _P, _ST, _P, _ST, C.POINTER(Options), C.POINTER(Scratch), _P],
 }
 EXPORTS = ["pbs_last_error_string", "pbs_version", "pbs_launch_count"] + list(SIGNATURES)

@@ -21,9 +21,12 @@
 // columns P_h vacated.  So while a softmax warpgroup works on one half, the MMAs of the other half
 // (and of the other query tile) run, and the next S is ready when the warpgroup comes back for it.
 // One issuer's barrier bookkeeping overlaps the other issuer's MMAs.
-// Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag, all roles leave
-// their loops, TMEM is freed and status[0] tells the host.
+// Every wait on an mbarrier is bounded (2 s unless pbs_debug_set_attn_wait says otherwise); when one
+// runs out the CTA raises a flag, all roles leave their loops, in-flight copies and MMAs are waited
+// out (bounded), TMEM is freed and status[0] tells the host which wait it was.
 #include <cuda.h>
+
+#include <atomic>
 
 #include "pbs_common.cuh"
 
@@ -204,23 +207,6 @@ template <> struct PackP<PBS_FP16> {
   }
 };
 
-// Optional timeline trace (compiled in with -DPBS_TC_TRACE only): CTA 0 records clock64() stamps of
-// its MMA issuer and of lane 0 of each softmax warpgroup's first warp.
-#ifdef PBS_TC_TRACE
-__device__ long long g_trace[4][4096];
-__device__ int g_trace_n[4];
-#define PBS_TRACE_DECL int trace_n__ = 0
-#define PBS_TRACE(role, tag)                                                                     \
-  do {                                                                                           \
-    if (blockIdx.x == 0 && trace_n__ < 4096) g_trace[role][trace_n__++] = (clock64() << 4) | (tag); \
-  } while (0)
-#define PBS_TRACE_END(role) do { if (blockIdx.x == 0) g_trace_n[role] = trace_n__; } while (0)
-#else
-#define PBS_TRACE_DECL do { } while (0)
-#define PBS_TRACE(role, tag) do { } while (0)
-#define PBS_TRACE_END(role) do { } while (0)
-#endif
-
 // ---------------------------------------------------------------------------------------------
 // Shared-memory plan
 // ---------------------------------------------------------------------------------------------
@@ -229,6 +215,7 @@ struct Bars {
   uint64_t k_full[NK], k_empty[NK];
   uint64_t v_full[NV], v_empty[NV];
   uint64_t s_full[2][2], p_full[2][2], o_full[2][2];   // [query tile][key half]
+  uint64_t drain;                                       // teardown after an abort: both issuers' MMAs retired
 };
 
 struct Params {
@@ -241,11 +228,16 @@ struct Params {
   int bs;
   float scale_log2e;
   int32_t* status;
+  void* extra_out[PBS_MAX_OUT_REPLICAS];   // further destinations of the output (same strides), e.g. on peer GPUs
+  int n_extra;
+  unsigned long long wait_ns;   // limit of every device-side wait
+  int drop_arrive;              // diagnostic: CTA 0's first softmax warpgroup skips one arrive (a wait then runs out)
 };
 
 struct Ctl {
   uint32_t tmem_base;
   volatile int abort_flag;
+  unsigned long long wait_ns;
 };
 
 // Work order.  Within a head the query groups are taken in the order G-1, 0, G-2, 1, ... and a CTA
@@ -273,7 +265,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctl* ctl
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (ctl->abort_flag) return false;
-      if (global_timer_ns() - t0 > 2000000000ull) {      // 2 s
+      if (global_timer_ns() - t0 > ctl->wait_ns) {
         ctl->abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -328,7 +320,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     for (int i = 0; i < NK; ++i) { mbar_init(smem_u32(&bars->k_full[i]), 1); mbar_init(smem_u32(&bars->k_empty[i]), 2); }
     for (int i = 0; i < NV; ++i) { mbar_init(smem_u32(&bars->v_full[i]), 1); mbar_init(smem_u32(&bars->v_empty[i]), 2); }
+    mbar_init(smem_u32(&bars->drain), 2);
     ctl->abort_flag = 0;
+    ctl->wait_ns = p.wait_ns;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -407,7 +401,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
         }
       }
-      if (!ok) __nanosleep(200000);                       // let copies in flight land before teardown
     }
   } else if (warp == 1 || warp == 3) {
     // =========================================================================== MMA issuers
@@ -420,7 +413,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       const int i = warp >> 1;                              // query tile of this issuer
       uint32_t kc = 0, vc = 0, qc = 0, pc = 0;
       bool ok = true;
-      PBS_TRACE_DECL;
       const uint32_t use_bit = 1u << (16 + i);
 
       // Descriptors are built once; per instruction only a compile-time constant is added to the
@@ -486,11 +478,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int e = 0; e < n && ok; ++e) {
           const uint32_t nn = (e + 2 < n) ? lst[e + 2] : 0u;    // read two entries ahead of its use
           const uint32_t vs = vc % NV, ks = kc % NK;
-          if (lane == 0) PBS_TRACE(i, 6);
           ok = wait_bar_warp(smem_u32(&bars->v_full[vs]), (vc / NV) & 1u, ctl, p.status, 6);
           if (!ok) break;
           if (nxt) {
-            if (lane == 0) PBS_TRACE(i, 8);
             ok = wait_bar_warp(smem_u32(&bars->k_full[ks]), (kc / NK) & 1u, ctl, p.status, 8);
             if (!ok) break;
           }
@@ -499,17 +489,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int h = 0; h < 2 && ok; ++h) {
             if (cur & use_bit) {
-              if (lane == 0) PBS_TRACE(i, 0);
               ok = wait_bar_warp(smem_u32(&bars->p_full[i][h]), pc & 1u, ctl, p.status, 7);
               if (!ok) break;
-              if (lane == 0) PBS_TRACE(i, 1);
               tc_fence_after();
               issue_pv(vs, started || h == 1, h);
             }
             if (nxt & use_bit) {
               tc_fence_after();
               issue_qk(ks, h);
-              if (lane == 0) PBS_TRACE(i, 4);
             }
           }
           if (!ok) break;
@@ -529,7 +516,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!ok) break;
         if (have) tc_commit(smem_u32(&bars->q_empty[i]));
       }
-      if (lane == 0) PBS_TRACE_END(i);
+      // Abort path: this commit arrives once every MMA this warp issued has retired.
+      if (ctl->abort_flag) tc_commit(smem_u32(&bars->drain));
     }
   } else if (warp >= 4) {
     // =========================================================================== softmax + epilogue
@@ -543,7 +531,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t bar_o[2] = {smem_u32(&bars->o_full[i][0]), smem_u32(&bars->o_full[i][1])};
     uint32_t sc = 0;                                       // list entries done by this warpgroup
     bool ok = true;
-    PBS_TRACE_DECL;
 
     for (int it = 0, pos; (pos = item_position(it, p.n_items)) >= 0 && ok; ++it) {
       int bh, g;
@@ -580,11 +567,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // Two half-steps of 64 keys, each an ordinary online-softmax step on its own 64 columns of S.
 #pragma unroll
         for (int hs = 0; hs < 2; ++hs) {
-          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 0);
           ok = __all_sync(0xffffffffu, wait_bar(bar_s[hs], sc & 1u, ctl, p.status, 9));
           if (!ok) break;
           tc_fence_after();
-          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 1);
           const uint32_t s_addr = tmem_S[i] + lane_off + 64 * hs;
 
           // S_h is read from TMEM once and stays in registers for the maximum and the exponentiation.
@@ -613,7 +598,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             mx[a] = fmaxf(m, v[32 * a + 31]);
           }
           const float mt = fmaxf(mx[0], mx[1]) * p.scale_log2e;
-          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 2);
 
           float alpha = 1.f;
           if (mt > m_used + kRescaleThreshold) {           // also the first finite maximum
@@ -659,8 +643,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           }
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(bar_p[hs]);
-          if (wq == 0 && lane == 0) PBS_TRACE(2 + i, 3 + hs);
+          // diagnostic hook of the failure-path test: the very first hand-over of CTA 0 is withheld,
+          // so the issuer's wait for it runs out and the CTA takes the abort path
+          if (!(p.drop_arrive && blockIdx.x == 0 && i == 0 && sc == 0 && hs == 0)) mbar_arrive(bar_p[hs]);
           l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
         }
         if (!ok) break;
@@ -676,7 +661,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         tc_fence_after();
       }
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)qpos * p.os.s;
+      const int64_t ooff = (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)qpos * p.os.s;
+      T* orow = reinterpret_cast<T*>(p.out) + ooff;
 #pragma unroll
       for (int c = 0; c < D / 16; ++c) {
         uint32_t o[16];
@@ -696,19 +682,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
             w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
             __stcs(reinterpret_cast<uint4*>(orow + c * 16 + j * 8), w);   // written once, not re-read here
+            // replicas (peer GPUs of a head-sharded call): plain stores, they travel over NVLink
+            for (int x = 0; x < p.n_extra; ++x)
+              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.extra_out[x]) + ooff + c * 16 + j * 8) = w;
           }
         }
       }
       // the next item's first P V overwrites O_i: order our TMEM reads before the arrive that lets it go
       tc_fence_before();
     }
-    if (wq == 0 && lane == 0) PBS_TRACE_END(2 + i);
   }
 
   // =============================================================================== teardown
+  // After an abort, work may still be in flight when the roles leave their loops: TMA copies into
+  // this CTA's shared memory and MMAs into its TMEM.  Neither may outlive the CTA, so everybody
+  // first lets the copies land (a copy takes a few microseconds; 100 us, bounded) and the TMEM owner
+  // waits (bounded again) until both issuers' MMAs have retired before it frees the columns.
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (ctl->abort_flag) {
+    for (int n = 0; n < 100; ++n) __nanosleep(1000);
+    if (warp == 2) {
+      const uint64_t t0 = global_timer_ns();
+      while (!mbar_try_wait(smem_u32(&bars->drain), 0) && global_timer_ns() - t0 < 2000000ull) { }
+      tc_fence_after();
+    }
+    __syncthreads();
+  }
   if (warp == 2) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
@@ -717,6 +718,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
+// Limit of every device-side wait and the diagnostic hook, process wide (pbs_debug_set_attn_wait).
+std::atomic<unsigned long long> g_wait_ns{2000000000ull};
+std::atomic<int> g_drop_arrive{0};
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -747,7 +752,8 @@ int make_map(CUtensorMap* map, int dt, const void* base, int rank, const cuuint6
 
 template <int DT, int D>
 int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void* pv, const int32_t* idx,
-           const uint32_t* list, const int32_t* count, void* out, Strides os, int32_t* status, cudaStream_t st) {
+           const uint32_t* list, const int32_t* count, void* out, Strides os, int32_t* status,
+           const pbs_out_replicas_t* replicas, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   const cuuint64_t e = 2;
   {
@@ -777,13 +783,14 @@ int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void*
   p.scale_log2e = (float)(1.4426950408889634 / sqrt((double)d.D));
   p.status = status;
 
-  static int sm_count = 0;
-  if (!sm_count) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if (sm_count <= 0) sm_count = 148;
-  }
+  p.n_extra = replicas ? replicas->count : 0;
+  for (int x = 0; x < PBS_MAX_OUT_REPLICAS; ++x) p.extra_out[x] = x < p.n_extra ? replicas->out[x] : nullptr;
+  p.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+  p.drop_arrive = g_drop_arrive.load(std::memory_order_relaxed);
+  int dev = 0, sm_count = 0;                               // of the device this launch goes to
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      sm_count <= 0)
+    sm_count = 148;
   auto kern = attn_tc_kernel<DT, D>;
   const int smem = Smem<D>::kTotal;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -797,15 +804,10 @@ int run_tc(const Dims& d, const void* q, Strides qs, const void* pk, const void*
 
 }  // namespace
 
-#ifdef PBS_TC_TRACE
-extern "C" int pbs_debug_read_trace(long long* host_buf, int* counts) {
-  cudaMemcpyFromSymbol(host_buf, g_trace, sizeof(long long) * 4 * 4096);
-  cudaMemcpyFromSymbol(counts, g_trace_n, sizeof(int) * 4);
-  int zero[4] = {0, 0, 0, 0};
-  cudaMemcpyToSymbol(g_trace_n, zero, sizeof(zero));
-  return 0;
+void set_attn_wait(unsigned long long wait_ns, int drop_arrive) {
+  g_wait_ns.store(wait_ns ? wait_ns : 2000000000ull, std::memory_order_relaxed);
+  g_drop_arrive.store(drop_arrive ? 1 : 0, std::memory_order_relaxed);
 }
-#endif
 
 bool attn_tc_supported(const Dims& d, int dt) {
   return (dt == PBS_BF16 || dt == PBS_FP16) && (d.D == 64 || d.D == 128) && (d.bs == 64 || d.bs == 128) &&
@@ -814,13 +816,13 @@ bool attn_tc_supported(const Dims& d, int dt) {
 
 int launch_attn_tc(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,
                    const int32_t* idx, const uint32_t* list, const int32_t* count, void* out, Strides os,
-                   int32_t* status, cudaStream_t st) {
+                   int32_t* status, const pbs_out_replicas_t* replicas, cudaStream_t st) {
   if (dt == PBS_BF16) {
-    if (d.D == 128) return run_tc<PBS_BF16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
-    return run_tc<PBS_BF16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+    if (d.D == 128) return run_tc<PBS_BF16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, replicas, st);
+    return run_tc<PBS_BF16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, replicas, st);
   }
-  if (d.D == 128) return run_tc<PBS_FP16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
-  return run_tc<PBS_FP16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, st);
+  if (d.D == 128) return run_tc<PBS_FP16, 128>(d, q, qs, pk, pv, idx, list, count, out, os, status, replicas, st);
+  return run_tc<PBS_FP16, 64>(d, q, qs, pk, pv, idx, list, count, out, os, status, replicas, st);
 }
 
 }  // namespace pbs

@@ -200,13 +200,15 @@ int launch_rope(int dt, int B, int H, int S, int D, void* x, Strides xs, const v
 int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void* pooled_k,
                          const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, float* scores,
                          cudaStream_t st);
+void set_select_impl(int impl);
 int launch_fill_mask_ones(const Dims& d, uint8_t* mask, cudaStream_t st);
 int launch_build_tile_lists(const Dims& d, const uint8_t* mask, uint32_t* list, int32_t* count, cudaStream_t st);
 int launch_attn_simt(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,
                      const int32_t* idx, const uint8_t* mask, void* out, Strides os, cudaStream_t st);
 bool attn_tc_supported(const Dims& d, int dt);
+void set_attn_wait(unsigned long long wait_ns, int drop_arrive);
 int launch_attn_tc(const Dims& d, int dt, const void* q, Strides qs, const void* pk, const void* pv,
                    const int32_t* idx, const uint32_t* list, const int32_t* count, void* out, Strides os,
-                   int32_t* status, cudaStream_t st);
+                   int32_t* status, const pbs_out_replicas_t* replicas, cudaStream_t st);
 
 }  // namespace pbs

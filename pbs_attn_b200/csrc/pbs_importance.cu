@@ -5,34 +5,74 @@
 // sqrt(D)), the softmax runs in fp32 over all keys of the complete segments, and the mean over the
 // block's query rows is an fp32 sum in the reference's summation order.
 //
-// Three kernels:
-//   logits_kernel     (L/64 x B*Hq CTAs)  logits tile -> scratch, per-tile row max / sum(exp)
-//   rowstats_kernel   (B*Hq CTAs)         merges the per-tile statistics into one (max, sum) per row
-//   importance_kernel (L/256 x B*Hq CTAs) mean_r exp(logit - max_r) / sum_r
-// HBM traffic per (b, h): K read once (L*D*e), logits written once and read once (2*bs*L*e),
-// importance written once (4*L).
+// The logits never reach HBM: the softmax is taken in two passes that each RECOMPUTE the last
+// block's logits from K (same instructions, same order, hence the same bits):
+//   pass 1  score kernel<1>   per 64-key tile and query row: max and sum(exp) of the tile -> partials
+//           rowstats_kernel   merges the per-tile pairs into one (max, sum) per row
+//   pass 2  score kernel<2>   p = exp(logit - max_r) / sum_r, summed over the rows r in the order of
+//                             the reference's reduction (16-row groups, then the groups) -> importance
+// HBM traffic per (b, h): K read once per pass (the query heads of a KV group run next to each other
+// and share its tiles in L2), the last query block, the per-tile statistics (16 bytes per row and
+// 64 keys) and the importance written once (4*L).
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
+
 #include "pbs_common.cuh"
 
 namespace pbs {
 namespace {
 
-constexpr int TM = 64;   // query rows per pass
-constexpr int TN = 64;   // keys per CTA
-constexpr int KC = 32;   // head-dim chunk staged in shared memory
+constexpr int TM = 64;   // query rows per pass of the CUDA-core kernel
+constexpr int TN = 64;   // keys per tile
+constexpr int KC = 32;   // head-dim chunk staged in shared memory (CUDA-core kernel)
 constexpr int LDT = TM + 4;
-constexpr int kMmaTilesPerCta = 4;   // 64-key tiles per CTA of the tensor-core logits kernel
-constexpr int kStageLd = TN + 8;     // elements per row of the per-warp output staging tile
+constexpr int kStageLd = TN + 8;     // elements per row of the per-warp logits staging tile
+constexpr int kPLd = TN + 8;         // floats per row of the probability tile: 8-byte stores of the MMA layout
+                                     // (8 rows x 4 pairs per instruction) and column reads are both conflict free
+constexpr int kMaxGroups = 16;       // 16-row groups of a block of up to 256 rows
 
-template <int DT>
+// Column sums of a tile of probabilities in the order of the reference's CPU reduction: rows are
+// added one after the other inside groups of 16; the caller adds the group sums one after the other.
+// 256 threads: thread t owns key t % 64 and the 16-row groups (t / 64) * gpt .. + gpt - 1 of this pass.
+__device__ __forceinline__ void group_sums(const float* P, float* gs, int rows_in_pass, int first_group, int gpt) {
+  const int key = threadIdx.x & (TN - 1), part = threadIdx.x >> 6;
+  for (int gg = 0; gg < gpt; ++gg) {
+    const int g = part * gpt + gg;
+    if (g * 16 >= rows_in_pass) break;
+    float a0 = 0.f;
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) a0 += P[(g * 16 + rr) * kPLd + key];
+    gs[(first_group + g) * TN + key] = a0;
+  }
+}
+
+// importance of the tile's keys from the group sums (level 1 of the cascade, then the mean)
+__device__ __forceinline__ void finish_tile(const float* gs, float* __restrict__ importance, int64_t out0, int nkeys, int bs) {
+  if (threadIdx.x < TN && (int)threadIdx.x < nkeys) {
+    float a1 = 0.f;
+    for (int g = 0; g < bs / 16; ++g) a1 += gs[g * TN + threadIdx.x];
+    importance[out0 + threadIdx.x] = a1 / (float)bs;
+  }
+}
+
+// CUDA-core kernel (fp32 inputs, or 16-bit inputs whose layout the tensor-core kernel cannot read).
+// One CTA = one 64-key tile x all rows of the last block, 64 rows per pass.
+template <int DT, int PASS>
 __global__ void __launch_bounds__(256)
-logits_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
-              const typename Elem<DT>::T* __restrict__ k, Strides ks,
-              typename Elem<DT>::T* __restrict__ logits, float2* __restrict__ partials,
-              int Hq, int group, int S, int D, int bs, int L, float sqrt_d) {
+score_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
+             const typename Elem<DT>::T* __restrict__ k, Strides ks,
+             float2* __restrict__ partials, const float2* __restrict__ rowstats, float* __restrict__ importance,
+             typename Elem<DT>::T* __restrict__ logits_out,
+             int Hq, int group, int S, int D, int bs, int L, float sqrt_d) {
   using E = Elem<DT>;
   using T = typename E::T;
   __shared__ __align__(16) float Qs[KC][LDT];
   __shared__ __align__(16) float Ks[KC][LDT];
+  __shared__ __align__(16) float P[PASS == 2 ? TM * kPLd : 4];
+  __shared__ float gs[PASS == 2 ? kMaxGroups * TN : 1];
+  __shared__ float2 stats[PASS == 2 ? 256 : 1];
 
   const int jt = blockIdx.x;
   const int bh = blockIdx.y;
@@ -45,6 +85,8 @@ logits_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int lrow = threadIdx.x >> 2;          // row / key this thread stages
   const int lcol = (threadIdx.x & 3) * 8;     // first of its 8 head-dim elements
+  if (PASS == 2)
+    for (int r = threadIdx.x; r < bs; r += blockDim.x) stats[r] = rowstats[(int64_t)bh * bs + r];
 
   for (int r0 = 0; r0 < bs; r0 += TM) {
     const int nrows = min(TM, bs - r0);
@@ -81,40 +123,57 @@ logits_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
       }
     }
 
-    // round like the reference, store, and reduce the tile's row statistics
+    // round like the reference; pass 1: the tile's row statistics, pass 2: probabilities
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = r0 + ty * 4 + i;
       float y[4];
-      float m = -CUDART_INF_F;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        y[j] = E::rnd(E::rnd(acc[i][j]) / sqrt_d);
-        if (tx * 4 + j < nkeys) m = fmaxf(m, y[j]);
-      }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      float z = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (tx * 4 + j < nkeys) z += expf(y[j] - m);
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
-      if (r < bs) {
-        T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN + tx * 4;
+      for (int j = 0; j < 4; ++j) y[j] = E::rnd(E::rnd(acc[i][j]) / sqrt_d);
+      if (PASS == 1) {
+        float m = -CUDART_INF_F;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (tx * 4 + j < nkeys) dst[j] = E::cvt(y[j]);
-        if (tx == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+          if (tx * 4 + j < nkeys) m = fmaxf(m, y[j]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float z = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (tx * 4 + j < nkeys) z += expf(y[j] - m);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+        if (r < bs) {
+          if (logits_out) {
+            T* dst = logits_out + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN + tx * 4;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (tx * 4 + j < nkeys) dst[j] = E::cvt(y[j]);
+          }
+          if (tx == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+        }
+      } else {
+        const float2 st = stats[min(r, bs - 1)];
+        *reinterpret_cast<float4*>(&P[(ty * 4 + i) * kPLd + tx * 4]) =
+            make_float4(expf(y[0] - st.x) / st.y, expf(y[1] - st.x) / st.y, expf(y[2] - st.x) / st.y, expf(y[3] - st.x) / st.y);
       }
     }
+    if (PASS == 2) {
+      __syncthreads();
+      group_sums(P, gs, nrows, r0 >> 4, 1);
+    }
+  }
+  if (PASS == 2) {
+    __syncthreads();
+    finish_tile(gs, importance, (int64_t)bh * L + (int64_t)jt * TN, nkeys, bs);
   }
 }
 
-// Tensor-core variant of logits_kernel for 16-bit inputs (mma.sync m16n8k16, fp32 accumulate: the
-// products of 16-bit values are exact and the sum is rounded like any fp32 GEMM).  One CTA = 64 keys x
-// all query rows of the last block (128 per pass); warp w owns rows 16w..16w+15 of the pass.  Q and K
-// tiles sit in shared memory with 16 bytes of padding per row so ldmatrix is conflict free.
+// Tensor-core kernel for 16-bit inputs (mma.sync m16n8k16, fp32 accumulate: the products of 16-bit
+// values are exact and the sum is rounded like any fp32 GEMM).  A CTA keeps the whole last query
+// block in shared memory and walks `tiles_per_cta` consecutive 64-key tiles, the next tile arriving
+// by cp.async while the current one is multiplied; warp w owns rows 16w..16w+15 of a 128-row pass.
+// Rows are padded by 16 bytes so ldmatrix is conflict free.
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -129,57 +188,111 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int DT>
-__global__ void __launch_bounds__(256)
-logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
-                  const typename Elem<DT>::T* __restrict__ k, Strides ks,
-                  typename Elem<DT>::T* __restrict__ logits, float2* __restrict__ partials,
-                  int Hq, int group, int S, int D, int bs, int L, int ntile, float sqrt_d) {
+// x / z for a divisor used many times: reciprocal product corrected by one exact-remainder step (the
+// correctly rounded quotient for all but a few divisors with an all-ones significand, where the result
+// may differ from it in the last bit).
+__device__ __forceinline__ float div_by(float x, float z, float rz) {
+  const float qv = x * rz;
+  return fmaf(fmaf(-qv, z, x), rz, qv);
+}
+
+// FASTDIV: rounding a * (1 / sqrt(D)) to the input type gives the same bits as rounding a / sqrt(D)
+// for EVERY value a of that type (established on the host by trying all 65536 of them)
+template <int DT, int PASS, bool FASTDIV>
+__global__ void __launch_bounds__(256, PASS == 1 ? 3 : 2)
+score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
+                 const typename Elem<DT>::T* __restrict__ k, Strides ks,
+                 float2* __restrict__ partials, const float2* __restrict__ rowstats, float* __restrict__ importance,
+                 typename Elem<DT>::T* __restrict__ logits_out,
+                 int Hq, int group, int S, int D, int bs, int L, int ntile, int tiles_per_cta, float sqrt_d) {
   using E = Elem<DT>;
   using T = typename E::T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int ld = D + 8;                                    // padded row length in elements
-  T* Qs = reinterpret_cast<T*>(smem_raw);                  // [128][ld]
-  T* Ks = Qs + 128 * ld;                                   // [64][ld]
-  T* stage = Ks + TN * ld;                                 // [8 warps][16 rows][kStageLd]
+  const int qrows = (bs + 127) & ~127;                     // staged query rows (whole 128-row passes)
+  T* Qs = reinterpret_cast<T*>(smem_raw);                  // [qrows][ld]
+  T* Ks = Qs + qrows * ld;                                 // [2][64][ld]
+  unsigned char* extra = reinterpret_cast<unsigned char*>(Ks + 2 * TN * ld);
+  T* stage = reinterpret_cast<T*>(extra);                  // pass 1 with logits_out: [8 warps][16 rows][kStageLd]
+  float* P = reinterpret_cast<float*>(extra);              // pass 2: [8 warps][8 rows][kPLd], private to each warp
+  float* gs = P + 64 * kPLd;                               //         [2][kMaxGroups][64] group sums, double buffered
+  float3* stats = reinterpret_cast<float3*>(gs + 2 * kMaxGroups * TN);   // [bs] (max, sum, 1 / sum)
 
-  const int bh = blockIdx.y;
-  const int b = bh / Hq, h = bh % Hq;
+  // the query heads of a KV group sit next to each other in the grid: they read the same K tiles
+  const int hin = blockIdx.x % group, chunk = blockIdx.x / group;
+  const int Hkv = Hq / group;
+  const int b = blockIdx.y / Hkv, hkv = blockIdx.y % Hkv;
+  const int h = hkv * group + hin;
+  const int bh = b * Hq + h;
   const T* qbase = q + (int64_t)b * qs.b + (int64_t)h * qs.h + (int64_t)(S - bs) * qs.s;
+  const T* khead = k + (int64_t)b * ks.b + (int64_t)hkv * ks.h;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cpr = D / 8;                                   // 16-byte chunks per row
+  const int jt0 = chunk * tiles_per_cta;
+  const int ntiles_here = min(tiles_per_cta, ntile - jt0);
+  if (ntiles_here <= 0) return;
 
-  // The query rows are staged once per pass and reused for kMmaTilesPerCta key tiles.
-  for (int r0 = 0; r0 < bs; r0 += 128) {
-    const int nrows = min(128, bs - r0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < 128 * cpr; i += blockDim.x) {
-      const int r = i / cpr, c = i % cpr;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (r < nrows) val = *reinterpret_cast<const uint4*>(qbase + (int64_t)(r0 + r) * qs.s + c * 8);
-      *reinterpret_cast<uint4*>(Qs + r * ld + c * 8) = val;
-    }
-   for (int it = 0; it < kMmaTilesPerCta; ++it) {
-    const int jt = blockIdx.x * kMmaTilesPerCta + it;
-    if (jt >= ntile) break;
-    const T* kbase = k + (int64_t)b * ks.b + (int64_t)(h / group) * ks.h + (int64_t)jt * TN * ks.s;
+  auto load_k = [&](int buf, int jt) {
     const int nkeys = min(TN, L - jt * TN);
-    __syncthreads();                                       // previous tile's K fully consumed
+    const T* kbase = khead + (int64_t)jt * TN * ks.s;
     for (int i = threadIdx.x; i < TN * cpr; i += blockDim.x) {
       const int r = i / cpr, c = i % cpr;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (r < nkeys) val = *reinterpret_cast<const uint4*>(kbase + (int64_t)r * ks.s + c * 8);
-      *reinterpret_cast<uint4*>(Ks + r * ld + c * 8) = val;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Ks + (buf * TN + r) * ld + c * 8);
+      const T* src = kbase + (int64_t)min(r, nkeys - 1) * ks.s + c * 8;
+      const int bytes = r < nkeys ? 16 : 0;                // rows past the end are filled with zeros
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // importance of a finished tile from its group sums: the groups added one after the other, then the mean
+  auto finish_tile = [&](int it) {
+    if (threadIdx.x < TN) {
+      const int jt = jt0 + it;
+      const float* g0 = gs + (it & 1) * kMaxGroups * TN + threadIdx.x;
+      float a1 = 0.f;
+      for (int g = 0; g < bs / 16; ++g) a1 += g0[g * TN];
+      if ((int)threadIdx.x < min(TN, L - jt * TN)) importance[(int64_t)bh * L + (int64_t)jt * TN + threadIdx.x] = a1 / (float)bs;
+    }
+  };
+
+  load_k(0, jt0);
+  for (int i = threadIdx.x; i < qrows * cpr; i += blockDim.x) {
+    const int r = i / cpr, c = i % cpr;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r < bs) val = *reinterpret_cast<const uint4*>(qbase + (int64_t)r * qs.s + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * ld + c * 8) = val;
+  }
+  if (PASS == 2)
+    for (int r = threadIdx.x; r < bs; r += blockDim.x) {
+      const float2 st = rowstats[(int64_t)bh * bs + r];
+      stats[r] = make_float3(st.x, st.y, 1.f / st.y);
+    }
+
+  const float rinv = 1.f / sqrt_d;
+  // One block-wide barrier per tile: it publishes tile `it` (copied during the previous iteration) and
+  // the previous tile's group sums, and it tells that every warp is done with the other K buffer, which
+  // the copy of tile it + 1 then overwrites while this tile is multiplied.
+  for (int it = 0; it < ntiles_here; ++it) {
+    const int jt = jt0 + it;
+    const int buf = it & 1;
+    const int nkeys = min(TN, L - jt * TN);
+    const bool full = nkeys == TN;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
-    if (warp * 16 < nrows) {
+    if (it + 1 < ntiles_here) load_k(buf ^ 1, jt + 1);
+    if (PASS == 2 && it > 0) finish_tile(it - 1);
+    const T* Kt = Ks + buf * TN * ld;
+    float* gcur = gs + buf * kMaxGroups * TN;
+    for (int r0 = 0; r0 < bs; r0 += 128) {
+      const int nrows = min(128, bs - r0);
+      if (warp * 16 >= nrows) continue;
       float acc[8][4];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int t = 0; t < 4; ++t) acc[j][t] = 0.f;
-      const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (warp * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
-      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Ks + ((lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+      const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (r0 + warp * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
+      const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Kt + ((lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
       for (int d0 = 0; d0 < D; d0 += 16) {
         uint32_t a[4];
         ldmatrix_x4(a, q_addr + d0 * 2);
@@ -192,70 +305,87 @@ logits_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
         }
       }
       // this thread: rows lane/4 and lane/4 + 8 of the warp's 16, keys 8j + 2(lane%4), +1
-      const bool full = nkeys == TN;
-      const float rinv = 1.f / sqrt_d;
+      float* Pw = P + warp * 8 * kPLd;
+      float colsum[2] = {0.f, 0.f};                        // keys lane and lane + 32 of the tile, rows added in order
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = r0 + warp * 16 + (lane >> 2) + 8 * half;
+        const int lr = (lane >> 2) + 8 * half;             // row inside the warp's 16
+        const int r = r0 + warp * 16 + lr;
         float y[16];
-        float m = -CUDART_INF_F;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            // a / sqrt_d in fp32: reciprocal product corrected by one exact-remainder step, which
-            // gives the correctly rounded quotient; then the second rounding to the input type
+            // a / sqrt_d in fp32 (the correctly rounded quotient), then the second rounding to the input type
             const float a = E::rnd(acc[j][2 * half + t]);
-            float qv = a * rinv;
-            qv = fmaf(fmaf(-qv, sqrt_d, a), rinv, qv);
-            y[2 * j + t] = E::rnd(qv);
-            if (full || 8 * j + 2 * (lane & 3) + t < nkeys) m = fmaxf(m, y[2 * j + t]);
+            y[2 * j + t] = E::rnd(FASTDIV ? a * rinv : div_by(a, sqrt_d, rinv));
           }
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        float z = 0.f;
+        if (PASS == 1) {
+          float m = -CUDART_INF_F;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 8; ++j)
 #pragma unroll
-          for (int t = 0; t < 2; ++t)
-            if (full || 8 * j + 2 * (lane & 3) + t < nkeys) z += __expf(y[2 * j + t] - m);
-        z += __shfl_xor_sync(0xffffffffu, z, 1);
-        z += __shfl_xor_sync(0xffffffffu, z, 2);
-        // the rounded logits go through a per-warp staging tile (rows padded by 8 elements, which
-        // spreads the eight rows of a store over all banks) and leave as 16-byte pieces
-        T* srow = stage + (warp * 16 + (lane >> 2) + 8 * half) * kStageLd;
+            for (int t = 0; t < 2; ++t)
+              if (full || 8 * j + 2 * (lane & 3) + t < nkeys) m = fmaxf(m, y[2 * j + t]);
+          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+          float z = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          T pair[2] = {E::cvt(y[2 * j]), E::cvt(y[2 * j + 1])};
-          *reinterpret_cast<uint32_t*>(srow + 8 * j + 2 * (lane & 3)) = *reinterpret_cast<const uint32_t*>(pair);
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+              if (full || 8 * j + 2 * (lane & 3) + t < nkeys) z += __expf(y[2 * j + t] - m);
+          z += __shfl_xor_sync(0xffffffffu, z, 1);
+          z += __shfl_xor_sync(0xffffffffu, z, 2);
+          if (r < bs && (lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
+          if (logits_out) {
+            // inspection output: the rounded logits leave through a per-warp staging tile
+            T* srow = stage + (warp * 16 + lr) * kStageLd;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              T pair[2] = {E::cvt(y[2 * j]), E::cvt(y[2 * j + 1])};
+              *reinterpret_cast<uint32_t*>(srow + 8 * j + 2 * (lane & 3)) = *reinterpret_cast<const uint32_t*>(pair);
+            }
+          }
+        } else {
+          // The warp's 16 rows are exactly one 16-row group of the reduction.  Its probabilities pass
+          // through the warp's own tile, 8 rows at a time, so that each lane can add up two key
+          // columns row after row.
+          const float3 st = stats[min(r, bs - 1)];
+          float* prow = Pw + (lane >> 2) * kPLd + 2 * (lane & 3);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float2*>(prow + 8 * j) =
+                make_float2(div_by(expf(y[2 * j] - st.x), st.y, st.z), div_by(expf(y[2 * j + 1] - st.x), st.y, st.z));
+          __syncwarp();
+#pragma unroll
+          for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) colsum[kk] += Pw[rr * kPLd + lane + 32 * kk];
+          __syncwarp();
         }
-        if (r < bs && (lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
       }
       __syncwarp();
-      if (full) {
-        // four rows per store instruction: 8 lanes x 16 bytes cover the 64 keys of a row
-#pragma unroll
-        for (int rr = 0; rr < 16; rr += 4) {
-          const int lr = rr + (lane >> 3);
-          const int r = r0 + warp * 16 + lr;
-          if (r < bs) {
-            T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN + (lane & 7) * 8;
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(stage + (warp * 16 + lr) * kStageLd + (lane & 7) * 8);
-          }
-        }
-      } else {
+      if (PASS == 1 && logits_out) {
 #pragma unroll 4
         for (int rr = 0; rr < 16; ++rr) {
           const int r = r0 + warp * 16 + rr;
           if (r < bs && 2 * lane < nkeys) {
-            T* dst = logits + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
+            T* dst = logits_out + ((int64_t)bh * bs + r) * L + (int64_t)jt * TN;
             *reinterpret_cast<uint32_t*>(dst + 2 * lane) = *reinterpret_cast<const uint32_t*>(stage + (warp * 16 + rr) * kStageLd + 2 * lane);
           }
         }
       }
-      __syncwarp();
+      if (PASS == 2) {
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) gcur[((r0 >> 4) + warp) * TN + lane + 32 * kk] = colsum[kk];
+      }
+      __syncwarp();                                        // the warp's staging / probability tile is free again
     }
-   }
+  }
+  if (PASS == 2) {
+    __syncthreads();
+    finish_tile(ntiles_here - 1);
   }
 }
 
@@ -288,35 +418,43 @@ rowstats_kernel(const float2* __restrict__ partials, float2* __restrict__ rowsta
   if (lane == 0) rowstats[(int64_t)bh * bs + r] = make_float2(m, z);
 }
 
+// Does rounding a * (1 / sqrt_d) to the 16-bit type T give the bits of rounding a / sqrt_d for every a?
+// Tried once per (type, head_dim) over all 65536 bit patterns, on the host, with the device's arithmetic
+// (IEEE fp32 product and quotient, round-to-nearest-even conversions).
 template <int DT>
-__global__ void __launch_bounds__(256)
-importance_kernel(const typename Elem<DT>::T* __restrict__ logits, const float2* __restrict__ rowstats,
-                  float* __restrict__ importance, int bs, int L) {
-  using E = Elem<DT>;
-  extern __shared__ float2 stats[];
-  const int bh = blockIdx.y;
-  for (int r = threadIdx.x; r < bs; r += blockDim.x) stats[r] = rowstats[(int64_t)bh * bs + r];
-  __syncthreads();
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= L) return;
-  const typename E::T* col = logits + (int64_t)bh * bs * L + j;
-  CascadeSum sum;
-  int r = 0;
-  for (; r + 8 <= bs; r += 8) {                      // eight loads in flight per thread
-    float y[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) y[u] = E::ld(col + (int64_t)(r + u) * L);
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const float2 st = stats[r + u];
-      sum.add(expf(y[u] - st.x) / st.y);
+bool mul_equals_div(int D) {
+  static std::mutex mu;
+  static std::map<int, bool> known;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = known.find(D);
+  if (it != known.end()) return it->second;
+  const float sq = (float)sqrt((double)D);
+  const volatile float rinv = 1.f / sq;
+  bool same = true;
+  for (uint32_t bits = 0; bits < 65536u && same; ++bits) {
+    float a;
+    uint16_t want, got;
+    if (DT == PBS_BF16) {
+      const uint32_t w = bits << 16;
+      memcpy(&a, &w, 4);
+      if (!std::isfinite(a)) continue;
+      const volatile float quot = a / sq, prod = a * rinv;
+      const __nv_bfloat16 x = __float2bfloat16_rn(quot), y = __float2bfloat16_rn(prod);
+      memcpy(&want, &x, 2); memcpy(&got, &y, 2);
+    } else {
+      __half hv;
+      const uint16_t hb = (uint16_t)bits;
+      memcpy(&hv, &hb, 2);
+      a = __half2float(hv);
+      if (!std::isfinite(a)) continue;
+      const volatile float quot = a / sq, prod = a * rinv;
+      const __half x = __float2half_rn(quot), y = __float2half_rn(prod);
+      memcpy(&want, &x, 2); memcpy(&got, &y, 2);
     }
+    same = want == got;
   }
-  for (; r < bs; ++r) {
-    const float2 st = stats[r];
-    sum.add(expf(E::ld(col + (int64_t)r * L) - st.x) / st.y);
-  }
-  importance[(int64_t)bh * L + j] = sum.total() / (float)bs;
+  known[D] = same;
+  return same;
 }
 
 template <int DT>
@@ -326,27 +464,46 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
   const int BH = d.B * d.Hq;
   const int ntile = (d.L + TN - 1) / TN;
   const float sq = (float)sqrt((double)d.D);
-  if (DT != PBS_FP32 && d.D % 16 == 0 && qs.s % 8 == 0 && ks.s % 8 == 0) {
-    // 16-bit inputs: tensor cores
-    auto kern = logits_mma_kernel<DT>;
-    const size_t smem = ((size_t)(128 + TN) * (d.D + 8) + 8 * 16 * kStageLd) * sizeof(T);
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return cuda_fail(e, "logits_mma_kernel smem attribute");
+  const bool mma = DT != PBS_FP32 && d.D % 16 == 0 && qs.s % 8 == 0 && ks.s % 8 == 0 && d.bs % 16 == 0;
+  // enough CTAs to fill the GPU a few times over, long enough runs of tiles to amortise the query block
+  int tiles_per_cta = 16;
+  while (tiles_per_cta > 1 && (int64_t)((ntile + tiles_per_cta - 1) / tiles_per_cta) * BH < 592) tiles_per_cta >>= 1;
+  const int chunks = (ntile + tiles_per_cta - 1) / tiles_per_cta;
+  const int qrows = (d.bs + 127) & ~127;
+  const size_t smem_base = (size_t)(qrows + 2 * TN) * (d.D + 8) * sizeof(T);
+  const size_t smem1 = smem_base + (logits ? (size_t)8 * 16 * kStageLd * sizeof(T) : 0);
+  const size_t smem2 = smem_base + (size_t)(64 * kPLd + 2 * kMaxGroups * TN) * sizeof(float) + (size_t)d.bs * sizeof(float3);
+  bool fastdiv = false;
+  if constexpr (DT != PBS_FP32) fastdiv = mma && mul_equals_div<DT>(d.D);
+
+  for (int pass = 1; pass <= 2; ++pass) {
+    if constexpr (DT != PBS_FP32) {
+      if (mma) {
+        auto kern = pass == 1 ? (fastdiv ? score_mma_kernel<DT, 1, true> : score_mma_kernel<DT, 1, false>)
+                              : (fastdiv ? score_mma_kernel<DT, 2, true> : score_mma_kernel<DT, 2, false>);
+        const size_t smem = pass == 1 ? smem1 : smem2;
+        if (smem > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+          if (e != cudaSuccess) return cuda_fail(e, "score_mma_kernel smem attribute");
+        }
+        kern<<<dim3(chunks * d.group, d.B * d.Hkv), 256, smem, st>>>(
+            (const T*)q, qs, (const T*)k, ks, (float2*)partials, (const float2*)rowstats, importance,
+            pass == 1 ? (T*)logits : nullptr, d.Hq, d.group, d.S, d.D, d.bs, d.L, ntile, tiles_per_cta, sq);
+        PBS_CUDA_CHECK_LAUNCH("score_mma_kernel");
+      }
     }
-    kern<<<dim3((ntile + kMmaTilesPerCta - 1) / kMmaTilesPerCta, BH), 256, smem, st>>>(
-        (const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq, d.group, d.S, d.D, d.bs, d.L, ntile, sq);
-    PBS_CUDA_CHECK_LAUNCH("logits_mma_kernel");
-  } else {
-    logits_kernel<DT><<<dim3(ntile, BH), 256, 0, st>>>(
-        (const T*)q, qs, (const T*)k, ks, (T*)logits, (float2*)partials, d.Hq, d.group, d.S, d.D, d.bs, d.L, sq);
-    PBS_CUDA_CHECK_LAUNCH("logits_kernel");
+    if (!mma) {
+      auto kern = pass == 1 ? score_kernel<DT, 1> : score_kernel<DT, 2>;
+      kern<<<dim3(ntile, BH), 256, 0, st>>>(
+          (const T*)q, qs, (const T*)k, ks, (float2*)partials, (const float2*)rowstats, importance,
+          pass == 1 ? (T*)logits : nullptr, d.Hq, d.group, d.S, d.D, d.bs, d.L, sq);
+      PBS_CUDA_CHECK_LAUNCH("score_kernel");
+    }
+    if (pass == 1) {
+      rowstats_kernel<<<dim3((d.bs + 7) / 8, BH), 256, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
+      PBS_CUDA_CHECK_LAUNCH("rowstats_kernel");
+    }
   }
-  rowstats_kernel<<<dim3((d.bs + 7) / 8, BH), 256, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
-  PBS_CUDA_CHECK_LAUNCH("rowstats_kernel");
-  importance_kernel<DT><<<dim3((d.L + 255) / 256, BH), 256, d.bs * sizeof(float2), st>>>(
-      (const T*)logits, (const float2*)rowstats, importance, d.bs, d.L);
-  PBS_CUDA_CHECK_LAUNCH("importance_kernel");
   return PBS_OK;
 }
 

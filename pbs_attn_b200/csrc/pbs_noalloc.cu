@@ -3,8 +3,8 @@
 // Some hosts of this library can hand it only their input and output buffers: a plugin boundary
 // that owns all device memory itself, or a serving loop that is forbidden to call cudaMalloc once it
 // is running because an allocation may synchronise the whole device and stall other streams.  For
-// them this entry point keeps the stage's scratch (the rounded last-block logits and the per-tile
-// and per-row softmax statistics) in a fixed array that is part of the library image.
+// them this entry point keeps the stage's scratch (the per-tile and per-row softmax statistics of
+// the last query block) in a fixed array that is part of the library image.
 //
 // The array costs PBS_STATIC_SCRATCH_BYTES (64 MiB) of device memory on every GPU that loads the
 // library, for the life of the process.  Calls whose scratch would not fit are rejected.
@@ -32,11 +32,9 @@ extern "C" int pbs_key_importance_static(const pbs_shape_t* shape, const void* q
   pbs_scratch_sizes_t z;
   int rc = pbs_scratch_sizes(shape, &z);               // validates the shape
   if (rc != PBS_OK) return rc;
-  const size_t e = (size_t)pbs::elem_bytes(shape->dtype);
-  const size_t logits_bytes = round256((size_t)z.logits * e);
   const size_t partials_bytes = round256((size_t)z.partials * sizeof(float2));
   const size_t rowstats_bytes = round256((size_t)z.rowstats * sizeof(float2));
-  const size_t need = logits_bytes + partials_bytes + rowstats_bytes;
+  const size_t need = partials_bytes + rowstats_bytes;
   if (need > (size_t)PBS_STATIC_SCRATCH_BYTES) {
     pbs::set_error("pbs_key_importance_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
                    "use pbs_key_importance with caller-provided scratch",
@@ -59,8 +57,7 @@ extern "C" int pbs_key_importance_static(const pbs_shape_t* shape, const void* q
     }
     base = g_scratch_ptr[dev];
   }
-  // Every byte the stage reads from its scratch is written earlier in the same call (logits, tile
+  // Every byte the stage reads from its scratch is written earlier in the same call (tile
   // statistics, row statistics), so nothing has to be cleared between calls.
-  return pbs_key_importance(shape, q, q_strides, k, k_strides, base, base + logits_bytes,
-                            base + logits_bytes + partials_bytes, importance, stream);
+  return pbs_key_importance(shape, q, q_strides, k, k_strides, nullptr, base, base + partials_bytes, importance, stream);
 }

@@ -11,6 +11,8 @@
 // One CTA per (q block, b, h).  Scores never reach HBM: a row of up to 4096 blocks lives in shared
 // memory.  HBM traffic per (b, h): pooled Q and K read (2*nb*D*e, K re-read from L2 per row), the
 // mask written once (nb*nb bytes).
+#include <atomic>
+
 #include "pbs_common.cuh"
 
 namespace pbs {
@@ -23,7 +25,7 @@ template <int DT, int KPT>
 __global__ void __launch_bounds__(SEL_THREADS)
 select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename Elem<DT>::T* __restrict__ pooled_k,
               const int32_t* __restrict__ first_block, const float* __restrict__ thr_per_head, float thr_scalar,
-              int select_all, int force_first, int diag_candidates, uint8_t* __restrict__ mask,
+              int select_all, int force_first, int diag_candidates, int own_segment, uint8_t* __restrict__ mask,
               float* __restrict__ scores, int Hq, int D, int nb, int bps, float sqrt_d, int npow2_max) {
   using E = Elem<DT>;
   using T = typename E::T;
@@ -188,8 +190,245 @@ select_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename 
   }
   __syncthreads();
   if (force_first && threadIdx.x == 0) row[first_block[bh]] = 1;
-  const int s0 = (qb / bps) * bps, s1 = min(s0 + bps, nb);
-  for (int i = s0 + threadIdx.x; i < s1; i += blockDim.x) row[i] = 1;
+  if (own_segment) {
+    const int s0 = (qb / bps) * bps, s1 = min(s0 + bps, nb);
+    for (int i = s0 + threadIdx.x; i < s1; i += blockDim.x) row[i] = 1;
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Tiled variant: one CTA = 16 consecutive q blocks of one (b, h).
+//
+// Phase A computes the pooled logits of the 16 rows against 64-kv-block chunks of pooled K that
+// arrive in shared memory by cp.async (each pooled-K row is then read once per 16 rows instead of
+// once per row).  The dot product keeps the summation order of select_kernel: 16-byte pieces are
+// summed front to back, the piece sums are combined in the order of a butterfly over the pieces.
+// Phases B-D run one warp per row: fp32 softmax (the exponent sum is taken in the same order as the
+// 256-thread reduction of select_kernel), then the cut of the cumulative-threshold selection is
+// found WITHOUT sorting: the bits of the cut probability are fixed one at a time, each step summing
+// (in double) the probabilities at or above the trial value; blocks above the cut are kept, blocks
+// equal to it are added in kv-block order until the running sum reaches the threshold -- the set a
+// stable descending sort followed by a running sum selects.
+// ---------------------------------------------------------------------------------------------
+constexpr int TS_ROWS = 16;       // q blocks per CTA
+constexpr int TS_CHUNK = 64;      // kv blocks per staged chunk
+
+template <int N>
+__device__ __forceinline__ float butterfly_sum(float (&p)[N]) {
+  // the value lane 0 of an N-lane xor-butterfly (offsets N/2 .. 1) ends up with
+#pragma unroll
+  for (int o = N / 2; o > 0; o >>= 1)
+#pragma unroll
+    for (int c = 0; c < o; ++c) p[c] = p[c] + p[c ^ o];
+  return p[0];
+}
+
+__device__ __forceinline__ double warp_sum_double(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// CPR: 16-byte pieces per pooled row; KPT: kv blocks per lane held in registers (32 * KPT >= nb)
+template <int DT, int CPR, int KPT>
+__global__ void __launch_bounds__(256)
+select_tiled_kernel(const typename Elem<DT>::T* __restrict__ pooled_q, const typename Elem<DT>::T* __restrict__ pooled_k,
+                    const int32_t* __restrict__ first_block, const float* __restrict__ thr_per_head, float thr_scalar,
+                    int select_all, int force_first, int diag_candidates, int own_segment, uint8_t* __restrict__ mask,
+                    float* __restrict__ scores, int Hq, int nb, int bps, float sqrt_d, int ncpad) {
+  using E = Elem<DT>;
+  using T = typename E::T;
+  constexpr int EPV = 16 / (int)sizeof(T);
+  constexpr int D = CPR * EPV;
+  constexpr int LDK = D + EPV;                             // padded pooled-K row in shared memory
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* Qs = reinterpret_cast<float*>(smem_raw);          // [16][D] fp32
+  T* Kc = reinterpret_cast<T*>(Qs + TS_ROWS * D);          // [2][64][LDK]
+  T* lg = Kc + 2 * TS_CHUNK * LDK;                         // [16][ncpad] rounded logits
+
+  const int qb0 = blockIdx.x * TS_ROWS;
+  const int bh = blockIdx.y;
+  const int h = bh % Hq;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int qb_last = min(qb0 + TS_ROWS, nb) - 1;
+  const int ncmax = diag_candidates ? qb_last + 1 : (qb_last / bps) * bps;   // candidates of the tile's last row
+  const T* kbase = pooled_k + (int64_t)bh * nb * D;
+  const int nchunks = select_all ? 0 : (ncmax + TS_CHUNK - 1) / TS_CHUNK;
+
+  auto load_chunk = [&](int buf, int c) {
+    for (int i = threadIdx.x; i < TS_CHUNK * CPR; i += blockDim.x) {
+      const int r = i / CPR, pc = i % CPR;
+      const int kb = c * TS_CHUNK + r;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Kc + (buf * TS_CHUNK + r) * LDK + pc * EPV);
+      const T* src = kbase + (int64_t)min(kb, nb - 1) * D + pc * EPV;
+      const int bytes = kb < nb ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  if (nchunks > 0) load_chunk(0, 0);
+  for (int i = threadIdx.x; i < TS_ROWS * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    Qs[i] = qb0 + r < nb ? E::ld(pooled_q + ((int64_t)bh * nb + qb0 + r) * D + d) : 0.f;
+  }
+
+  // ---- phase A: logits.  Thread = (row, kv lane): row t / 16, kv blocks t % 16 + 16 a of the chunk.
+  const int arow = threadIdx.x >> 4, aj0 = threadIdx.x & 15;
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) {
+      load_chunk((c + 1) & 1, c + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const T* Kt = Kc + (c & 1) * TS_CHUNK * LDK;
+    const float* qr = Qs + arow * D;
+#pragma unroll
+    for (int a = 0; a < TS_CHUNK / 16; ++a) {
+      const int j = aj0 + 16 * a;
+      const int kb = c * TS_CHUNK + j;
+      if (kb >= ncmax) continue;
+      float piece[CPR];
+#pragma unroll
+      for (int pc = 0; pc < CPR; ++pc) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(Kt + j * LDK + pc * EPV);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        float acc = 0.f;
+#pragma unroll
+        for (int t = 0; t < EPV; ++t) acc = fmaf(qr[pc * EPV + t], E::ld(e + t), acc);
+        piece[pc] = acc;
+      }
+      const float dot = butterfly_sum<CPR>(piece);
+      lg[arow * ncpad + kb] = E::cvt(E::rnd(E::rnd(dot) / sqrt_d));
+    }
+    __syncthreads();
+  }
+  if (nchunks == 0) __syncthreads();
+
+  // ---- phases B-D: one warp per row (rows 2 * warp and 2 * warp + 1)
+  const float thr = thr_per_head ? thr_per_head[h] : thr_scalar;
+  for (int rr = 0; rr < TS_ROWS / 8; ++rr) {
+    const int r = warp * (TS_ROWS / 8) + rr;
+    const int qb = qb0 + r;
+    if (qb >= nb) break;
+    const int ncand = diag_candidates ? qb + 1 : (qb / bps) * bps;
+    const int kmax = (ncand + 31) >> 5;                    // register slots in use
+    uint8_t* row = mask + ((int64_t)bh * nb + qb) * nb;
+    float* srow = scores ? scores + ((int64_t)bh * nb + qb) * nb : nullptr;
+    unsigned long long sel = 0ull;                         // bit k: candidate 32 k + lane is kept
+
+    if (select_all) {
+#pragma unroll
+      for (int k = 0; k < KPT; ++k)
+        if (32 * k + lane < ncand) sel |= 1ull << k;
+    } else if (ncand > 0) {
+      // fp32 softmax over the candidates
+      float pv[KPT];
+      float m = -CUDART_INF_F;
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) {
+        pv[k] = -CUDART_INF_F;
+        if (k < kmax && 32 * k + lane < ncand) pv[k] = E::ld(lg + r * ncpad + 32 * k + lane);
+        m = fmaxf(m, pv[k]);
+      }
+      m = warp_max(m);
+      // exponent sum in the order of a 256-thread strided reduction: 8 interleaved accumulators,
+      // each reduced over the lanes, then added up one after the other
+      float zacc[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) zacc[w] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) {
+        const bool valid = k < kmax && 32 * k + lane < ncand;
+        const float e = valid ? expf(pv[k] - m) : 0.f;
+        pv[k] = e;
+        if (valid) zacc[k & 7] += e;
+      }
+      float z = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) z += warp_sum(zacc[w]);
+      float pmax = 0.f;
+#pragma unroll
+      for (int k = 0; k < KPT; ++k) {
+        const bool valid = k < kmax && 32 * k + lane < ncand;
+        float p = pv[k] / z;
+        if (p != p) p = 0.f;                               // nan_to_num
+        if (!valid) p = 0.f;
+        pv[k] = p;
+        pmax = fmaxf(pmax, p);
+        if (srow && valid) srow[32 * k + lane] = p;
+      }
+      pmax = warp_max(pmax);
+
+      // total mass: if even that stays below the threshold nothing is selected
+      double tot = 0.0;
+#pragma unroll
+      for (int k = 0; k < KPT; ++k)
+        if (k < kmax) tot += (double)pv[k];
+      tot = warp_sum_double(tot);
+      if ((float)tot >= thr) {
+        // cut = largest probability value v with (float) sum{p >= v} >= thr (bit pattern order)
+        const uint32_t umax = __float_as_uint(pmax);
+        uint32_t cut = umax;
+        if (thr > 0.f && umax != 0u) {
+          cut = 0u;
+          for (int b = 31 - __clz(umax); b >= 0; --b) {
+            const uint32_t cand = cut | (1u << b);
+            if (cand > umax) continue;
+            double g = 0.0;
+#pragma unroll
+            for (int k = 0; k < KPT; ++k)
+              if (k < kmax && __float_as_uint(pv[k]) >= cand) g += (double)pv[k];
+            g = warp_sum_double(g);
+            if ((float)g >= thr) cut = cand;
+          }
+        }
+        // everything above the cut; then the blocks equal to it, in kv-block order, until reached
+        double run = 0.0;
+#pragma unroll
+        for (int k = 0; k < KPT; ++k) {
+          const bool valid = k < kmax && 32 * k + lane < ncand;
+          if (valid && __float_as_uint(pv[k]) > cut) { run += (double)pv[k]; sel |= 1ull << k; }
+        }
+        run = warp_sum_double(run);
+        const double pcut = (double)__uint_as_float(cut);
+        bool done = false;
+#pragma unroll
+        for (int k = 0; k < KPT; ++k) {
+          if (k >= kmax) break;
+          const bool valid = 32 * k + lane < ncand;
+          unsigned ties = __ballot_sync(0xffffffffu, valid && __float_as_uint(pv[k]) == cut);
+          while (ties && !done) {
+            const int l = __ffs(ties) - 1;
+            ties &= ties - 1;
+            run += pcut;
+            if (lane == l) sel |= 1ull << k;
+            if ((float)run >= thr) done = true;
+          }
+          if (done) break;
+        }
+      }
+    } else if (thr <= 0.f) {
+      // no candidate: every score is 0 and a non-positive threshold is met at rank 0 (kv block 0)
+      if (lane == 0) sel |= 1ull;
+    }
+
+    // ---- write the row: selection, first-token block, own segment
+    const int fb = force_first ? first_block[bh] : -1;
+    const int s0 = own_segment ? (qb / bps) * bps : 0, s1 = own_segment ? min(s0 + bps, nb) : 0;
+    const bool no_cand_rule = !select_all && ncand == 0;   // the kept block is kv block 0 even with no candidate
+    for (int k = 0; 32 * k < nb; ++k) {
+      const int i = 32 * k + lane;
+      if (i >= nb) break;
+      bool on = (k < KPT) && ((sel >> k) & 1ull) && (i < ncand || no_cand_rule);
+      on = on || i == fb || (i >= s0 && i < s1);
+      row[i] = on ? 1 : 0;
+      if (srow && (select_all || i >= ncand)) srow[i] = 0.f;
+    }
+  }
 }
 
 __global__ void fill_ones_kernel(uint8_t* p, int64_t n) {
@@ -253,11 +492,69 @@ tile_list_kernel(const uint8_t* __restrict__ mask, uint32_t* __restrict__ list, 
   if (threadIdx.x == 0) count[(int64_t)bh * ngroups + g] = wbase;
 }
 
+template <int DT, int CPR, int KPT>
+int run_select_tiled(const Dims& d, const void* pooled_q, const void* pooled_k, const int32_t* first_block,
+                     const pbs_options_t& opt, uint8_t* mask, float* scores, cudaStream_t st) {
+  using T = typename Elem<DT>::T;
+  constexpr int EPV = 16 / (int)sizeof(T);
+  const int ncpad = ((d.nb + TS_CHUNK - 1) / TS_CHUNK) * TS_CHUNK;
+  const size_t smem = (size_t)TS_ROWS * d.D * sizeof(float) + (size_t)2 * TS_CHUNK * (d.D + EPV) * sizeof(T) +
+                      (size_t)TS_ROWS * ncpad * sizeof(T);
+  auto kern = select_tiled_kernel<DT, CPR, KPT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "select_tiled_kernel smem attribute");
+  }
+  kern<<<dim3((d.nb + TS_ROWS - 1) / TS_ROWS, d.B * d.Hq), 256, smem, st>>>(
+      (const T*)pooled_q, (const T*)pooled_k, first_block, opt.threshold_per_head, opt.threshold, opt.select_all,
+      opt.force_select_first_block, opt.diagonal_candidates, opt.no_own_segment ? 0 : 1, mask, scores, d.Hq, d.nb, d.bps,
+      (float)sqrt((double)d.D), ncpad);
+  PBS_CUDA_CHECK_LAUNCH("select_tiled_kernel");
+  return PBS_OK;
+}
+
+template <int DT, int CPR>
+int run_select_tiled_k(const Dims& d, const void* pooled_q, const void* pooled_k, const int32_t* first_block,
+                       const pbs_options_t& opt, uint8_t* mask, float* scores, cudaStream_t st) {
+  if (d.nb <= 256) return run_select_tiled<DT, CPR, 8>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st);
+  if (d.nb <= 512) return run_select_tiled<DT, CPR, 16>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st);
+  if (d.nb <= 1024) return run_select_tiled<DT, CPR, 32>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st);
+  return run_select_tiled<DT, CPR, 64>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st);
+}
+
+// The tiled kernel covers pooled rows of 8, 16 or 32 16-byte pieces and up to 2048 blocks per row.
+bool select_tiled_supported(const Dims& d, int dt) {
+  const int cpr = d.D * elem_bytes(dt) / 16;
+  return d.nb <= 2048 && (d.D * elem_bytes(dt)) % 16 == 0 && (cpr == 8 || cpr == 16 || cpr == 32);
+}
+
+int launch_select_tiled(const Dims& d, int dt, const void* pooled_q, const void* pooled_k, const int32_t* first_block,
+                        const pbs_options_t& opt, uint8_t* mask, float* scores, cudaStream_t st) {
+  const int cpr = d.D * elem_bytes(dt) / 16;
+#define PBS_TS(DT)                                                                                                \
+  (cpr == 8 ? run_select_tiled_k<DT, 8>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st)                 \
+   : cpr == 16 ? run_select_tiled_k<DT, 16>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st)             \
+               : run_select_tiled_k<DT, 32>(d, pooled_q, pooled_k, first_block, opt, mask, scores, st))
+  switch (dt) {
+    case PBS_BF16: return PBS_TS(PBS_BF16);
+    case PBS_FP16: return PBS_TS(PBS_FP16);
+    default: return PBS_TS(PBS_FP32);
+  }
+#undef PBS_TS
+}
+
 }  // namespace
+
+namespace {
+std::atomic<int> g_select_impl{0};     // 0: tiled where supported; 1: always the one-row-per-CTA kernel
+}
+void set_select_impl(int impl) { g_select_impl.store(impl, std::memory_order_relaxed); }
 
 int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void* pooled_k,
                          const int32_t* first_block, const pbs_options_t& opt, uint8_t* mask, float* scores,
                          cudaStream_t st) {
+  if (g_select_impl.load(std::memory_order_relaxed) == 0 && select_tiled_supported(d, dt))
+    return launch_select_tiled(d, dt, pooled_q, pooled_k, first_block, opt, mask, scores, st);
   const int npow2 = next_pow2(d.nb);
   const size_t smem = (size_t)npow2 * 8 + (size_t)d.D * 4 + (size_t)d.nb * 4;
   dim3 grid(d.nb, d.B * d.Hq);
@@ -271,7 +568,8 @@ int launch_select_blocks(const Dims& d, int dt, const void* pooled_q, const void
     }                                                                                                         \
     kern<<<grid, SEL_THREADS, smem, st>>>((const TT*)pooled_q, (const TT*)pooled_k, first_block,              \
                                           opt.threshold_per_head, opt.threshold, opt.select_all,             \
-                                          opt.force_select_first_block, opt.diagonal_candidates, mask,       \
+                                          opt.force_select_first_block, opt.diagonal_candidates,             \
+                                          opt.no_own_segment ? 0 : 1, mask,                                  \
                                           scores, d.Hq, d.D, d.nb, d.bps, sq, npow2);                         \
   }
   // keys per thread of the register sort; beyond 16 the sort runs in shared memory

@@ -16,6 +16,7 @@ import torch
 from . import _cabi
 
 _DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.FP16, torch.float32: _cabi.FP32}
+_STATUS_SLOTS = 16      # whole-path calls whose status words may be in flight to the host at once
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -66,7 +67,8 @@ class Plan:
             return torch.empty(max(int(n), 1), dtype=dt, device=dev)
 
         B, H, S, D = batch, q_heads, seq_len, head_dim
-        self.logits = buf(0 if self.dense else sizes.logits, dtype)
+        self.logits = None                 # optional inspection output of stage 1a, allocated on demand
+        self._logits_numel = int(sizes.logits)
         self.partials = buf(0 if self.dense else 2 * sizes.partials, torch.float32)
         self.rowstats = buf(2 * sizes.rowstats, torch.float32)
         self.importance = buf(sizes.importance, torch.float32)
@@ -80,18 +82,53 @@ class Plan:
         self.tile_list = buf(sizes.tile_list, torch.int32)
         self.tile_count = buf(sizes.tile_count, torch.int32)
         self.status = torch.zeros(int(sizes.status), dtype=torch.int32, device=dev)
-        self.scratch = _cabi.Scratch(*[t.data_ptr() for t in (
-            self.logits, self.partials, self.rowstats, self.importance, self.key_indices, self.perm_k,
+        self.scratch = _cabi.Scratch(None, *[t.data_ptr() for t in (
+            self.partials, self.rowstats, self.importance, self.key_indices, self.perm_k,
             self.perm_v, self.pooled_q, self.pooled_k, self.first_block, self.block_mask, self.tile_list,
             self.tile_count, self.status)])
         self._thr_dev = None
+        # deferred status check: after every whole-path call the 8 status words are copied to pinned
+        # host memory (asynchronously); the copies that have landed are inspected on entry to the next call
+        self._status_ring = torch.zeros(_STATUS_SLOTS, 8, dtype=torch.int32).pin_memory()
+        self._status_pending = []          # [(event, slot)], oldest first
+        self._status_next = 0
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
+    def _on_device(self):
+        """The library launches on the CURRENT device: make this plan's device current around every call."""
+        return torch.cuda.device(self.device)
+
+    def _raise_status(self, words):
+        raise _cabi.PbsError(f"device-side error flags {list(words)}: a bounded wait in the attention kernel ran out "
+                             f"(code {int(words[0])}); the output of that call is invalid")
+
+    def _inspect_landed_status(self, wait_all: bool = False):
+        while self._status_pending:
+            ev, slot = self._status_pending[0]
+            if wait_all or len(self._status_pending) >= _STATUS_SLOTS:
+                ev.synchronize()
+            elif not ev.query():
+                break
+            self._status_pending.pop(0)
+            words = self._status_ring[slot].tolist()
+            if words[0] != 0:
+                self._status_pending.clear()
+                self._raise_status(words)
+
+    def _queue_status_copy(self):
+        slot = self._status_next
+        self._status_next = (slot + 1) % _STATUS_SLOTS
+        self._status_ring[slot].copy_(self.status, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._status_pending.append((ev, slot))
+
     def options(self, threshold, force_select_first_block=True, query_pool_mode="mean", key_pool_mode="mean",
-                attn_impl="auto", no_permutation=False, diagonal_candidates=False) -> _cabi.Options:
+                attn_impl="auto", no_permutation=False, diagonal_candidates=False, no_own_segment=False,
+                out_replicas: Optional[_cabi.OutReplicas] = None) -> _cabi.Options:
         for m in (query_pool_mode, key_pool_mode):
             if m not in _cabi.POOL:
                 raise ValueError(f"Invalid pool mode: {m}")
@@ -105,23 +142,32 @@ class Plan:
             select_all = 1          # the reference takes every candidate block for the int 1
         else:
             thr = float(threshold)
-        return _cabi.Options(thr_ptr, thr, select_all, int(bool(force_select_first_block)),
-                             _cabi.POOL[query_pool_mode], _cabi.POOL[key_pool_mode], _cabi.ATTN_IMPL[attn_impl],
-                             int(bool(no_permutation)), int(bool(diagonal_candidates)))
+        opt = _cabi.Options(thr_ptr, thr, select_all, int(bool(force_select_first_block)),
+                            _cabi.POOL[query_pool_mode], _cabi.POOL[key_pool_mode], _cabi.ATTN_IMPL[attn_impl],
+                            int(bool(no_permutation)), int(bool(diagonal_candidates)), int(bool(no_own_segment)),
+                            C.pointer(out_replicas) if out_replicas is not None else None)
+        opt._keep = out_replicas            # the struct must outlive the call
+        return opt
 
     def check_status(self):
-        """Synchronises and raises if a kernel reported a device-side error."""
+        """Synchronises and raises if a kernel reported a device-side error (in the last call or in an
+        earlier whole-path call whose status has not been inspected yet)."""
+        self._inspect_landed_status(wait_all=True)
         st = self.status.cpu()
         if int(st[0]) != 0:
-            raise _cabi.PbsError(f"device-side error flags {st.tolist()}: a bounded wait in the attention kernel ran out")
+            self._raise_status(st.tolist())
 
     # ------------------------------------------------------------------ stages
     def key_importance(self, q, k, want_logits: bool = False):
         """Returns the (B, Hq, L) importance; with ``want_logits`` also the (B, Hq, block_size, L)
         rounded scoring logits (for inspection and tests)."""
-        _cabi.check(self.lib.pbs_key_importance(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
-                                                _ptr(self.logits), _ptr(self.partials), _ptr(self.rowstats),
-                                                _ptr(self.importance), self._stream()), "pbs_key_importance")
+        if want_logits and self.logits is None:
+            self.logits = torch.empty(max(self._logits_numel, 1), dtype=self.dtype, device=self.device)
+        with self._on_device():
+            _cabi.check(self.lib.pbs_key_importance(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                                    _ptr(self.logits if want_logits else None), _ptr(self.partials),
+                                                    _ptr(self.rowstats), _ptr(self.importance), self._stream()),
+                        "pbs_key_importance")
         B, H, L = self.shape.batch, self.shape.q_heads, self.n_complete
         imp = self.importance[: B * H * L].view(B, H, L)
         if want_logits:
@@ -130,41 +176,51 @@ class Plan:
 
     def segment_permute(self, k, v, key_pool_mode="mean", identity=False):
         imp = None if identity else _ptr(self.importance)
-        _cabi.check(self.lib.pbs_segment_permute(C.byref(self.shape), imp, _ptr(k), _strides(k), _ptr(v), _strides(v),
-                                                 _ptr(self.key_indices), _ptr(self.perm_k), _ptr(self.perm_v),
-                                                 _ptr(self.pooled_k), _cabi.POOL[key_pool_mode],
-                                                 _ptr(self.first_block), self._stream()), "pbs_segment_permute")
+        with self._on_device():
+            _cabi.check(self.lib.pbs_segment_permute(C.byref(self.shape), imp, _ptr(k), _strides(k), _ptr(v), _strides(v),
+                                                     _ptr(self.key_indices), _ptr(self.perm_k), _ptr(self.perm_v),
+                                                     _ptr(self.pooled_k), _cabi.POOL[key_pool_mode],
+                                                     _ptr(self.first_block), self._stream()), "pbs_segment_permute")
 
     def pool_queries(self, q, query_pool_mode="mean"):
-        _cabi.check(self.lib.pbs_pool_queries(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.pooled_q),
-                                              _cabi.POOL[query_pool_mode], self._stream()), "pbs_pool_queries")
+        with self._on_device():
+            _cabi.check(self.lib.pbs_pool_queries(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.pooled_q),
+                                                  _cabi.POOL[query_pool_mode], self._stream()), "pbs_pool_queries")
 
     def select_blocks(self, opt: _cabi.Options, want_scores: bool = False):
         """Returns the (B, Hq, nb, nb) fp32 pooled scores when ``want_scores`` (else None)."""
         scores = None
         if want_scores:
             scores = torch.empty(self.block_mask.shape, dtype=torch.float32, device=self.device)
-        _cabi.check(self.lib.pbs_select_blocks(C.byref(self.shape), _ptr(self.pooled_q), _ptr(self.pooled_k),
-                                               _ptr(self.first_block), C.byref(opt), _ptr(self.block_mask),
-                                               _ptr(scores), self._stream()), "pbs_select_blocks")
+        with self._on_device():
+            _cabi.check(self.lib.pbs_select_blocks(C.byref(self.shape), _ptr(self.pooled_q), _ptr(self.pooled_k),
+                                                   _ptr(self.first_block), C.byref(opt), _ptr(self.block_mask),
+                                                   _ptr(scores), self._stream()), "pbs_select_blocks")
         return scores
 
     def build_tile_lists(self):
-        _cabi.check(self.lib.pbs_build_tile_lists(C.byref(self.shape), _ptr(self.block_mask), _ptr(self.tile_list),
-                                                  _ptr(self.tile_count), self._stream()), "pbs_build_tile_lists")
+        with self._on_device():
+            _cabi.check(self.lib.pbs_build_tile_lists(C.byref(self.shape), _ptr(self.block_mask), _ptr(self.tile_list),
+                                                      _ptr(self.tile_count), self._stream()), "pbs_build_tile_lists")
 
     def attn_fwd(self, q, out, attn_impl="auto"):
         self.status.zero_()
-        _cabi.check(self.lib.pbs_attn_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.perm_k), _ptr(self.perm_v),
-                                          _ptr(self.key_indices), _ptr(self.block_mask), _ptr(self.tile_list),
-                                          _ptr(self.tile_count), _ptr(out), _strides(out), _cabi.ATTN_IMPL[attn_impl],
-                                          _ptr(self.status), self._stream()), "pbs_attn_fwd")
+        with self._on_device():
+            _cabi.check(self.lib.pbs_attn_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(self.perm_k), _ptr(self.perm_v),
+                                              _ptr(self.key_indices), _ptr(self.block_mask), _ptr(self.tile_list),
+                                              _ptr(self.tile_count), _ptr(out), _strides(out), _cabi.ATTN_IMPL[attn_impl],
+                                              _ptr(self.status), None, self._stream()), "pbs_attn_fwd")
 
     # ------------------------------------------------------------------ whole path
     def run(self, q, k, v, out, opt: _cabi.Options):
-        _cabi.check(self.lib.pbs_prefill_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
-                                             _ptr(v), _strides(v), _ptr(out), _strides(out), C.byref(opt),
-                                             C.byref(self.scratch), self._stream()), "pbs_prefill_fwd")
+        """The whole path.  Never synchronises: a device-side error of an EARLIER call (its status words
+        have reached the host by now) is raised here; this call's own status is queued for the next."""
+        self._inspect_landed_status()
+        with self._on_device():
+            _cabi.check(self.lib.pbs_prefill_fwd(C.byref(self.shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                                 _ptr(v), _strides(v), _ptr(out), _strides(out), C.byref(opt),
+                                                 C.byref(self.scratch), self._stream()), "pbs_prefill_fwd")
+            self._queue_status_copy()
         return out
 
 
@@ -179,8 +235,9 @@ def key_importance_static(q: torch.Tensor, k: torch.Tensor, block_size: int, seg
     L = (S // segment_size) * segment_size
     out = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
     stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
-    _cabi.check(lib.pbs_key_importance_static(C.byref(shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
-                                              _ptr(out), stream), "pbs_key_importance_static")
+    with torch.cuda.device(q.device):       # the built-in array is looked up on, and used by, the current device
+        _cabi.check(lib.pbs_key_importance_static(C.byref(shape), _ptr(q), _strides(q), _ptr(k), _strides(k),
+                                                  _ptr(out), stream), "pbs_key_importance_static")
     return out
 
 
@@ -242,6 +299,8 @@ def permuted_block_sparse_attn_fwd(
     key_pool_mode: str = "mean",
     attn_impl: str = "auto",
     intermediates: Optional[dict] = None,
+    out: Optional[torch.Tensor] = None,
+    out_replicas: Optional[_cabi.OutReplicas] = None,
 ):
     """Permuted block-sparse attention forward (prefill, causal) on the CUDA library.
 
@@ -253,7 +312,11 @@ def permuted_block_sparse_attn_fwd(
       * ``use_triton`` is accepted and ignored (there is one backend);
       * ``attn_impl`` picks the attention kernel ("auto", "tcgen05", "simt");
       * ``intermediates``: a dict that receives the permutation, block mask and plan
-        (used by the parity tests).
+        (used by the parity tests);
+      * ``out``: a preallocated result tensor of q's shape and dtype (any strides the kernels can
+        write: unit head-dim stride, 16-byte aligned rows), e.g. a head slice of a larger tensor;
+      * ``out_replicas``: further destinations with ``out``'s strides that the attention kernel
+        writes as well (buffers on peer GPUs of a head-sharded call, see ``peer_gather``).
     Runs on the current CUDA stream without synchronising.
     """
     batch_size, num_q_heads, q_len, head_dim = query_states.shape
@@ -270,8 +333,12 @@ def permuted_block_sparse_attn_fwd(
     k = _readable(key_states)
     v = _readable(value_states)
     plan = get_plan(q, num_kv_heads, block_size, segment_size)
-    opt = plan.options(threshold, force_select_first_block, query_pool_mode, key_pool_mode, attn_impl)
-    out = torch.empty_like(q)
+    opt = plan.options(threshold, force_select_first_block, query_pool_mode, key_pool_mode, attn_impl,
+                       out_replicas=out_replicas)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or out.device != q.device:
+        raise ValueError("out must have the shape, dtype and device of query_states")
     plan.run(q, k, v, out, opt)
     if intermediates is not None:
         intermediates["plan"] = plan
@@ -302,15 +369,17 @@ def MeanPooling_prefill(
     keeps kv block 0 (``force_select_first_block``) and its own block, and attends causally.
     ``segment_size`` is accepted and unused, as in the reference.  Implemented as the permuted
     pipeline with identity key order, one block per segment and the diagonal block among the
-    candidates.  Additive: batch > 1 and Hkv < Hq are accepted; ``force_select_current_block=False``
-    and ``causal=False`` are not supported (the attention kernel always needs the diagonal block).
+    candidates.  With ``force_select_current_block=False`` the q block's own kv block is an ordinary
+    candidate (MeanPooling.py:55-58 skipped): a q block that does not select it does not attend it,
+    and a q block that selects nothing outputs zeros.  Additive: batch > 1 and Hkv < Hq are accepted.
+    ``causal=False`` is not supported (the attention kernels are causal).
     """
     batch_size, num_q_heads, q_len, head_dim = query_states.shape
     _, num_kv_heads, kv_len, _ = key_states.shape
     assert num_q_heads % num_kv_heads == 0
     assert q_len == kv_len, "Only support prefilling for now, q_len: {}, kv_len: {}".format(q_len, kv_len)
-    if not causal or not force_select_current_block:
-        raise NotImplementedError("MeanPooling_prefill on the CUDA library is causal and always keeps the current block")
+    if not causal:
+        raise NotImplementedError("MeanPooling_prefill on the CUDA library is causal")
     if not query_states.is_cuda:
         raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
     q = _readable(query_states, need_distinct_heads=True)
@@ -320,7 +389,7 @@ def MeanPooling_prefill(
     if not isinstance(threshold, torch.Tensor):
         threshold = float(threshold)        # the baseline has no "int 1 selects everything" rule
     opt = plan.options(threshold, force_select_first_block, "mean", "mean", attn_impl,
-                       no_permutation=True, diagonal_candidates=True)
+                       no_permutation=True, diagonal_candidates=True, no_own_segment=not force_select_current_block)
     out = torch.empty_like(q)
     plan.run(q, k, v, out, opt)
     if intermediates is not None:

@@ -96,3 +96,45 @@ def make_qkv(w: Workload, seed: int = 0, device="cpu", kv_heads: int | None = No
     apply_rope_(k, cos, sin)
     dt = w.torch_dtype
     return q.to(dt), k.to(dt), v.to(dt)
+
+
+def make_qkv_heads(w: Workload, seed: int, kv_start: int, kv_count: int, q_start: int | None = None,
+                   q_count: int | None = None, device="cpu"):
+    """The same kind of inputs as ``make_qkv``, drawn PER KV-HEAD GROUP so that a rank of a
+    head-sharded run generates exactly the heads it owns and every partition of the heads (1, 2, 4
+    or 8 ranks; query heads split inside a group) works on the same global problem.
+
+    Group j (KV head j with its query heads) comes from a generator seeded with (seed, j); the
+    shared direction ``u`` and the planted key positions come from a generator seeded with ``seed``.
+    Returns q (B, q_count, S, D) for the query heads [q_start, q_start + q_count) (default: all query
+    heads of the KV heads asked for) and k, v (B, kv_count, S, D).
+    """
+    B, S, D = w.batch, w.seq_len, w.head_dim
+    group = w.q_heads // w.kv_heads
+    if q_start is None:
+        q_start, q_count = kv_start * group, kv_count * group
+    g0 = torch.Generator(device=device).manual_seed(seed)
+    u = torch.randn(D, generator=g0, device=device)
+    u = u / u.norm()
+    pos = torch.randperm(S, generator=g0, device=device)[: int(round(w.density * S))]
+    cos, sin = rope_tables(S, D, w.rope_theta, device)
+    dt = w.torch_dtype
+    qs, ks, vs = [], [], []
+    for j in range(kv_start, kv_start + kv_count):
+        g = torch.Generator(device=device).manual_seed(seed * 1000003 + 7919 * (j + 1))
+        q = torch.randn(B, group, S, D, generator=g, device=device)
+        k = torch.randn(B, 1, S, D, generator=g, device=device)
+        v = torch.randn(B, 1, S, D, generator=g, device=device)
+        k[:, :, pos] += 3.0 * u
+        q += u
+        if w.sinks:
+            k[:, :, : w.sinks] += 5.0 * u
+        apply_rope_(q, cos, sin)
+        apply_rope_(k, cos, sin)
+        lo = max(q_start, j * group) - j * group
+        hi = min(q_start + q_count, (j + 1) * group) - j * group
+        if hi > lo:
+            qs.append(q[:, lo:hi].to(dt))
+        ks.append(k.to(dt))
+        vs.append(v.to(dt))
+    return torch.cat(qs, dim=1), torch.cat(ks, dim=1), torch.cat(vs, dim=1)

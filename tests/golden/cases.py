@@ -35,4 +35,10 @@ MEANPOOLING_CASES = {
     "meanpool_bf16_bs64_s1500": (Workload("meanpool_bf16_bs64_s1500", 1, 4, 2, 128, 1500, "bf16", 64, 64, 0.8, 1e6, density=0.05), 22, {}, 4),
     "meanpool_fp32_s1000": (Workload("meanpool_fp32_s1000", 2, 2, 2, 64, 1000, "fp32", 64, 64, 0.9, 1e4), 23,
                             {"force_select_first_block": False}, 4),
+    # the q block's own kv block is an ordinary candidate (force_select_current_block=False)
+    "meanpool_no_current_bf16": (Workload("meanpool_no_current_bf16", 1, 4, 1, 128, 2048, "bf16", 128, 128, 0.6, 5e5, sinks=4), 24,
+                                 {"force_select_current_block": False}, 8),
+    # ... and nothing forced at all with a threshold no row reaches: nothing is attended, the output is zero
+    "meanpool_nothing_fp32": (Workload("meanpool_nothing_fp32", 1, 2, 2, 64, 1000, "fp32", 64, 64, 1.5, 1e4), 25,
+                              {"force_select_first_block": False, "force_select_current_block": False}, 4),
 }

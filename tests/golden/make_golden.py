@@ -3,7 +3,7 @@
 Run once, on a machine that has the reference checked out (it is imported from the
 directory named by the REFERENCE_ROOT environment variable and is not needed afterwards):
 
-    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [--meanpooling-only]
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [--meanpooling-only] [--only=case,case]
 
 Per case two runs are stored: ``*_ref`` from the reference as it is (its sorts
 are non-stable: the order of tied items is implementation defined) and
@@ -111,6 +111,7 @@ class _BlockSparseAttnStub:
         elem = elem & torch.tril(torch.ones(S, S, dtype=torch.bool))
         logits = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / (D ** 0.5)
         p = torch.softmax(logits.masked_fill(~elem, float("-inf")), dim=-1)
+        p = torch.nan_to_num(p, nan=0.0)                     # rows without a visible key attend nothing: zeros
         return torch.einsum("hqk,khd->qhd", p, v.float()).to(q.dtype)
 
 
@@ -129,7 +130,10 @@ def make_meanpooling(make_qkv, cases):
         assert os.path.abspath(ref_mp.__file__).startswith(os.path.abspath(REFERENCE_ROOT)), ref_mp.__file__
     finally:
         sys.path.remove(REFERENCE_ROOT)
+    only = [a.split("=", 1)[1].split(",") for a in sys.argv if a.startswith("--only=")]
     for name, (w, seed, kwargs, stride) in cases.items():
+        if only and name not in only[0]:
+            continue
         q, k, v = make_qkv(w, seed)
         n_rep = w.q_heads // w.kv_heads
         kr, vr = k.repeat_interleave(n_rep, dim=1), v.repeat_interleave(n_rep, dim=1)

@@ -38,12 +38,14 @@ def test_meanpooling_against_reference_fixtures(name, impl):
     assert bad == 0, f"{bad}/{rows} mask rows unexplained"
     # the reference's selection run on OUR pooled scores must give our mask
     force = kwargs.get("force_select_first_block", True)
-    opt = plan.options(float(w.threshold), force, no_permutation=True, diagonal_candidates=True)
+    current = kwargs.get("force_select_current_block", True)
+    opt = plan.options(float(w.threshold), force, no_permutation=True, diagonal_candidates=True, no_own_segment=not current)
     scores = plan.select_blocks(opt, want_scores=True).cpu()
     expect = pbs_oracle.select_blocks(scores, float(w.threshold), stable=True)
     if force:
         expect[..., 0] = True
-    expect = expect | torch.eye(nb, dtype=torch.bool)[None, None]
+    if current:
+        expect = expect | torch.eye(nb, dtype=torch.bool)[None, None]
     rows2, bad2 = classify_mask(mask, expect, scores, float(w.threshold), 1)
     assert bad2 == 0, f"{bad2}/{rows2} rows differ from select_blocks run on our own scores"
     if w.dtype == "fp32":
@@ -94,4 +96,4 @@ def test_meanpooling_factory_and_patch_probe():
     assert "layer_idx" not in fn.func.__code__.co_varnames
     with pytest.raises(NotImplementedError):
         MeanPooling_prefill(torch.zeros(1, 1, 128, 64, device="cuda"), torch.zeros(1, 1, 128, 64, device="cuda"),
-                            torch.zeros(1, 1, 128, 64, device="cuda"), force_select_current_block=False)
+                            torch.zeros(1, 1, 128, 64, device="cuda"), causal=False)

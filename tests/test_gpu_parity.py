@@ -286,3 +286,64 @@ def test_host_buffer_call_equals_device_call():
                                                   w.segment_size, w.threshold, True, chunks=chunks)
         torch.cuda.synchronize()
         assert not got.is_cuda and torch.equal(got, want.cpu())
+
+
+@pytest.mark.parametrize("name", ["op_check_fp32", "llama_bf16_s4096", "qwen_bf16_bs64_seg128", "batch2_fp16", "max_pool",
+                                  "threshold_never_reached", "dense_int_threshold", "no_first_block"])
+def test_tiled_selection_kernel_equals_general_kernel(name):
+    """Stage 2b has two kernels: the tiled one (16 q blocks per CTA, cut found by bisection, used by
+    default where it applies) and the general one (one q block per CTA, full sort).  On identical pooled
+    inputs they must produce the same mask and the same pooled scores bit for bit."""
+    from pbs_attn_b200 import _cabi
+    lib = _cabi.load()
+    w, kwargs, stride, (q, k, v), g = load_case(name)
+    r = _oracle(w, kwargs, q, k, v)
+    qd, kd, vd = _dev(q, k, v)
+    plan = _plan(w, qd)
+    plan.importance[: r.importance.numel()].copy_(r.importance.reshape(-1).cuda())
+    kmode, qmode = kwargs.get("key_pool_mode", "mean"), kwargs.get("query_pool_mode", "mean")
+    plan.segment_permute(kd, vd, kmode)
+    plan.pool_queries(qd, qmode)
+    thresholds = [w.threshold] if isinstance(w.threshold, int) else [w.threshold, 0.5, 0.0, 1.0, torch.full((w.q_heads,), 0.8)]
+    for thr in thresholds:
+        for force in (True, False):
+            opt = plan.options(thr, force, qmode, kmode)
+            got = {}
+            try:
+                for impl in (0, 1):
+                    assert lib.pbs_debug_set_select_impl(impl) == 0
+                    scores = plan.select_blocks(opt, want_scores=True)
+                    torch.cuda.synchronize()
+                    got[impl] = (plan.block_mask.clone(), scores.clone())
+            finally:
+                lib.pbs_debug_set_select_impl(0)
+            assert torch.equal(got[0][0], got[1][0]), f"{name} thr={thr} force={force}: masks differ in {(got[0][0] != got[1][0]).sum().item()} bits"
+            assert torch.equal(got[0][1], got[1][1]), f"{name} thr={thr} force={force}: pooled scores differ"
+
+
+def test_output_replicas_receive_the_same_bytes():
+    """The attention kernel writes every output row to `out` and to each replica (the mechanism behind
+    the gather of a head-sharded call, where the replicas live on peer GPUs).  Here the replicas are
+    head slices of two larger tensors on the same GPU."""
+    from pbs_attn_b200 import _cabi
+    from pbs_attn_b200.prefill import permuted_block_sparse_attn_fwd
+    w, kwargs, stride, (q, k, v), g = load_case("llama_bf16_s4096")
+    qd, kd, vd = _dev(q, k, v)
+    want = permuted_block_sparse_attn_fwd(qd, kd, vd, w.block_size, w.segment_size, w.threshold, True)
+    full = [torch.zeros(w.batch, w.q_heads + 3, w.seq_len, w.head_dim, dtype=qd.dtype, device="cuda") for _ in range(3)]
+    out_view = full[0][:, 2:2 + w.q_heads]
+    rep = _cabi.OutReplicas()
+    rep.count = 2
+    for j in (0, 1):
+        rep.out[j] = full[1 + j][:, 2:2 + w.q_heads].data_ptr()
+    got = permuted_block_sparse_attn_fwd(qd, kd, vd, w.block_size, w.segment_size, w.threshold, True,
+                                         attn_impl="tcgen05", out=out_view, out_replicas=rep)
+    torch.cuda.synchronize()
+    assert got.data_ptr() == out_view.data_ptr()
+    for t in full:
+        assert torch.equal(t[:, 2:2 + w.q_heads], want)
+        assert not t[:, :2].any() and not t[:, 2 + w.q_heads:].any(), "rows outside the head range were written"
+    # the generic kernel cannot write replicas: rejected before anything is launched
+    with pytest.raises(_cabi.PbsError, match="replicas"):
+        permuted_block_sparse_attn_fwd(qd, kd, vd, w.block_size, w.segment_size, w.threshold, True,
+                                       attn_impl="simt", out=out_view, out_replicas=rep)

@@ -14,9 +14,9 @@ from pbs_attn_b200.synth import Workload, make_qkv
 
 def test_oversized_shape_is_rejected_without_touching_the_gpu():
     lib = _cabi.load()
-    # 32 heads x 128 rows x 131072 keys of bf16 logits = 1 GiB: far beyond the 64 MiB array
-    shape = _cabi.Shape(1, 32, 8, 131072, 128, 128, 256, _cabi.BF16)
-    st = _cabi.Strides4(131072 * 128 * 32, 131072 * 128, 128, 1)
+    # 32 heads x 8192 key tiles x 128 rows x 8 bytes of softmax statistics = 256 MiB: beyond the 64 MiB array
+    shape = _cabi.Shape(1, 32, 8, 524288, 128, 128, 256, _cabi.BF16)
+    st = _cabi.Strides4(524288 * 128 * 32, 524288 * 128, 128, 1)
     rc = lib.pbs_key_importance_static(C.byref(shape), C.c_void_p(1 << 20), st, C.c_void_p(1 << 21), st,
                                        C.c_void_p(1 << 22), None)
     assert rc == -1
