@@ -389,22 +389,47 @@ score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
   }
 }
 
-// One warp per (b, h, row): lanes stride the key tiles, each merging its (max, sum) pairs online,
-// then the 32 partial pairs are merged by shuffles.
-__global__ void __launch_bounds__(256)
+// Merges the per-tile (max, sum) pairs into one pair per (b, h, row).  Per row there are 32 running
+// pairs, pair l taking the tiles l, l + 32, ... one after the other, and the 32 pairs are then merged by a
+// butterfly.  One CTA = 32 rows: warp l owns the running pairs number l of all 32 rows, so that its loads
+// are 32 consecutive pairs (the statistics are stored tile-major, row-minor); the pairs then change hands
+// through shared memory, warp j taking the 32 pairs of row j for the butterfly.
+__global__ void __launch_bounds__(1024)
 rowstats_kernel(const float2* __restrict__ partials, float2* __restrict__ rowstats, int ntile, int bs) {
+  __shared__ float2 run[32][33];
   const int bh = blockIdx.y;
-  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (r >= bs) return;
-  const float2* p = partials + (int64_t)bh * ntile * bs + r;
-  float m = -CUDART_INF_F, z = 0.f;
-  for (int t = lane; t < ntile; t += 32) {
-    const float2 v = p[(int64_t)t * bs];
-    const float mn = fmaxf(m, v.x);
-    z = z * expf(m - mn) + v.y * expf(v.x - mn);
-    m = mn;
+  const int r0 = blockIdx.x * 32;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const int r = r0 + lane;
+    const float2* p = partials + (int64_t)bh * ntile * bs + r;
+    float m = -CUDART_INF_F, z = 0.f;
+    if (r < bs) {
+      int t = w;
+      for (; t + 32 * 3 < ntile; t += 32 * 4) {           // four loads in flight
+        float2 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = p[(int64_t)(t + 32 * u) * bs];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float mn = fmaxf(m, v[u].x);
+          z = z * expf(m - mn) + v[u].y * expf(v[u].x - mn);
+          m = mn;
+        }
+      }
+      for (; t < ntile; t += 32) {
+        const float2 v = p[(int64_t)t * bs];
+        const float mn = fmaxf(m, v.x);
+        z = z * expf(m - mn) + v.y * expf(v.x - mn);
+        m = mn;
+      }
+    }
+    run[w][lane] = make_float2(m, z);
   }
+  __syncthreads();
+  const int r = r0 + w;
+  if (r >= bs) return;
+  float m = run[lane][w].x, z = run[lane][w].y;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float mo = __shfl_xor_sync(0xffffffffu, m, o);
@@ -500,7 +525,7 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
       PBS_CUDA_CHECK_LAUNCH("score_kernel");
     }
     if (pass == 1) {
-      rowstats_kernel<<<dim3((d.bs + 7) / 8, BH), 256, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
+      rowstats_kernel<<<dim3((d.bs + 31) / 32, BH), 1024, 0, st>>>((const float2*)partials, (float2*)rowstats, ntile, d.bs);
       PBS_CUDA_CHECK_LAUNCH("rowstats_kernel");
     }
   }

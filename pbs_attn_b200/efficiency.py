@@ -18,7 +18,16 @@ Under ``torch.distributed.run`` the model is tensor-parallel the way the referen
 ``down_proj`` are summed over the ranks (one NCCL all-reduce each).  Random weights need no loading, so each rank
 simply builds the architecture with its share of the heads; the attention kernels see exactly a rank's heads.
 
-Prints one JSON line per context length.
+``--parallel dp`` is multi-sequence prefill instead: every rank holds the WHOLE model and its share of a batch
+of ``--batch`` sequences (default: one per rank; ``sharding.shard_batch``), nothing is exchanged while
+computing, a step ends when the slowest rank ends.  ``--attention-share`` times the same model a second
+time with attention replaced by a no-op and reports which share of the prefill the attention call is.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m pbs_attn_b200.efficiency \
+        --parallel dp --lens 65536 --attention-share --out results.jsonl
+
+Prints one JSON line per context length (rank 0) and appends it to ``--out`` when given, like the reference
+writes one result file per run (eval_efficiency.py:261-290).
 """
 import argparse
 import json
@@ -107,6 +116,9 @@ def no_attention(query_states, key_states, value_states):
     return query_states
 
 
+no_attention.takes_grouped_kv = True      # no repeat_kv copies either: they belong to the attention call being replaced
+
+
 def prefill_function(method: str, block_size: int, segment_size: int, threshold: float):
     from .hf_patch import get_meanpooling_prefill, get_permuted_block_sparse_attn_fwd
     if method == "pbs":
@@ -157,47 +169,80 @@ def main(argv=None):
     ap.add_argument("--slice-of", type=int, default=1, metavar="N",
                     help="on ONE GPU, run the slice one rank of an N-way tensor-parallel model holds, without the "
                          "all-reduces: the compute side of a multi-GPU point when no multi-GPU machine is at hand")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "dp"],
+                    help="under torch.distributed.run: tensor parallel (heads and MLP width split, the reference's "
+                         "tp_plan) or data parallel (whole model per rank, the batch split)")
+    ap.add_argument("--batch", type=int, default=None, help="sequences per step (data parallel: default one per rank)")
+    ap.add_argument("--attention-share", action="store_true",
+                    help="time the model a second time with attention replaced by a no-op and report the share")
+    ap.add_argument("--out", default=None, help="append the JSON lines to this file (rank 0)")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("the efficiency harness needs a CUDA device")
     import os
     import torch.distributed as dist
+    from .sharding import shard_batch
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from .hf_patch import apply_patch_with_prefill
+    from .hf_patch import apply_patch_with_prefill, remove_patch
     if args.slice_of > 1 and world > 1:
         raise SystemExit("--slice-of is for single-process runs")
-    model = build_model(args.arch, args.layers, device=f"cuda:{local_rank}", world=max(world, args.slice_of))
-    if world > 1:
+    tp = world if args.parallel == "tp" else 1
+    model = build_model(args.arch, args.layers, device=f"cuda:{local_rank}", world=max(tp, args.slice_of))
+    if tp > 1:
         add_row_parallel_reductions(model)
-    if args.method != "unpatched":
-        apply_patch_with_prefill(model, prefill_function(args.method, args.block_size, args.segment_size, args.threshold))
     model.generation_config.pad_token_id = 0
     vocab = model.get_input_embeddings().weight.size(0)
     dev = torch.device("cuda", local_rank)
-    gen = torch.Generator(device=dev).manual_seed(0)            # same ids on every rank
-    for length in [int(x) for x in args.lens.split(",")]:
-        ids = torch.randint(0, vocab, (1, length), device=dev, dtype=torch.long, generator=gen)
-        for _ in range(args.warmup):
-            measure_prefill_latency(model, ids)
-        times = [measure_prefill_latency(model, ids) for _ in range(args.iters)]
+    batch = args.batch or (world if args.parallel == "dp" else 1)
+    mine = shard_batch(batch, rank, world) if args.parallel == "dp" else slice(0, batch)
+    methods = [args.method] + (["noattn"] if args.attention_share and args.method != "noattn" else [])
+
+    def timed(method, ids):
+        remove_patch(model)
+        if method != "unpatched":
+            apply_patch_with_prefill(model, prefill_function(method, args.block_size, args.segment_size, args.threshold))
+        if ids.shape[0] == 0:                                   # a rank without a sequence of this batch
+            times = [0.0] * args.iters
+        else:
+            for _ in range(args.warmup):
+                measure_prefill_latency(model, ids)
+            times = [measure_prefill_latency(model, ids) for _ in range(args.iters)]
         if world > 1:                                            # a step ends when the slowest rank ends
             t = torch.tensor(times, dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             times = t.tolist()
+        return times
+
+    for length in [int(x) for x in args.lens.split(",")]:
+        gen = torch.Generator(device=dev).manual_seed(length)    # same ids on every rank
+        ids = torch.randint(0, vocab, (batch, length), device=dev, dtype=torch.long, generator=gen)[mine]
+        results = {m: timed(m, ids) for m in methods}
+        density = last_density() if args.method in ("pbs", "meanpooling") else None
         if rank != 0:
             continue
-        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers, "tp": world, "slice_of": args.slice_of,
-               "method": args.method, "len": length, "mean_s": sum(times) / len(times), "min_s": min(times),
+        times = results[args.method]
+        mean_s = sum(times) / len(times)
+        rec = {"metric": "prefill_latency_s", "arch": args.arch, "layers": model.config.num_hidden_layers,
+               "parallel": args.parallel if world > 1 else "none", "world": world, "tp": tp, "slice_of": args.slice_of,
+               "batch": batch, "method": args.method, "len": length, "mean_s": mean_s, "min_s": min(times),
+               "tokens_per_s": batch * length / mean_s,
                "iters": args.iters, "warmup": args.warmup, "weights": "random-init", "prompts": "uniform random ids",
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30}
         if args.method in ("pbs", "meanpooling"):
             rec.update(block_size=args.block_size, segment_size=args.segment_size, threshold=args.threshold,
-                       last_layer_density=last_density())
-        print(json.dumps(rec), flush=True)
+                       last_layer_density=density)
+        if "noattn" in results and args.method != "noattn":
+            rest = sum(results["noattn"]) / len(results["noattn"])
+            rec.update(without_attention_s=rest, attention_s=mean_s - rest, attention_share=(mean_s - rest) / mean_s)
+        line = json.dumps(rec)
+        print(line, flush=True)
+        if args.out:
+            with open(args.out, "a") as f:
+                f.write(line + "\n")
     if world > 1:
         dist.destroy_process_group()
 

@@ -94,10 +94,12 @@ def _kernel_of(prefill_fn):
 
 
 def _takes_grouped_kv(prefill_fn) -> bool:
-    """True for this package's own prefill function, which maps query heads onto fewer KV heads
-    itself; any other callable gets K/V repeated to the query head count like the reference does."""
+    """True for this package's own prefill functions, which map query heads onto fewer KV heads
+    themselves (and for a callable that says so with a ``takes_grouped_kv = True`` attribute); any
+    other callable gets K/V repeated to the query head count like the reference does."""
     from .prefill import MeanPooling_prefill, permuted_block_sparse_attn_fwd
-    return _kernel_of(prefill_fn) in (permuted_block_sparse_attn_fwd, MeanPooling_prefill)
+    kern = _kernel_of(prefill_fn)
+    return kern in (permuted_block_sparse_attn_fwd, MeanPooling_prefill) or bool(getattr(kern, "takes_grouped_kv", False))
 
 
 def patched_attention_forward(
@@ -189,4 +191,15 @@ def apply_patch_with_prefill(model, prefill_fn: Optional[Callable] = None, skip_
         attn.forward = types.MethodType(make_forward(prefill_fn), attn)
         patched += 1
     print(f"Patched {patched}/{len(layers)} attention layers.")
+    return model
+
+
+def remove_patch(model):
+    """Undoes ``apply_patch_with_prefill``: every patched layer gets its original forward back.
+    (The reference has no such call; re-patching a patched model there would keep the patched method
+    as ``original_forward``.  Used to time one model with several prefill functions.)"""
+    for layer in model.model.layers:
+        attn = layer.self_attn
+        if "original_forward" in attn.__dict__:
+            attn.forward = attn.__dict__.pop("original_forward")
     return model
