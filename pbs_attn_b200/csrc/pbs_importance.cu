@@ -15,6 +15,7 @@
 // and share its tiles in L2), the last query block, the per-tile statistics (16 bytes per row and
 // 64 keys) and the importance written once (4*L).
 #include <cmath>
+#include <type_traits>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -198,16 +199,18 @@ __device__ __forceinline__ float div_by(float x, float z, float rz) {
 
 // FASTDIV: rounding a * (1 / sqrt(D)) to the input type gives the same bits as rounding a / sqrt(D)
 // for EVERY value a of that type (established on the host by trying all 65536 of them)
-template <int DT, int PASS, bool FASTDIV>
+// DH: head_dim when it is 64 or 128 (loops unroll, index arithmetic folds), 0 = any multiple of 16
+template <int DT, int PASS, bool FASTDIV, int DH>
 __global__ void __launch_bounds__(256, PASS == 1 ? 3 : 2)
 score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
                  const typename Elem<DT>::T* __restrict__ k, Strides ks,
                  float2* __restrict__ partials, const float2* __restrict__ rowstats, float* __restrict__ importance,
                  typename Elem<DT>::T* __restrict__ logits_out,
-                 int Hq, int group, int S, int D, int bs, int L, int ntile, int tiles_per_cta, float sqrt_d) {
+                 int Hq, int group, int S, int D_rt, int bs, int L, int ntile, int tiles_per_cta, float sqrt_d) {
   using E = Elem<DT>;
   using T = typename E::T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = DH ? DH : D_rt;
   const int ld = D + 8;                                    // padded row length in elements
   const int qrows = (bs + 127) & ~127;                     // staged query rows (whole 128-row passes)
   T* Qs = reinterpret_cast<T*>(smem_raw);                  // [qrows][ld]
@@ -235,8 +238,9 @@ score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
   auto load_k = [&](int buf, int jt) {
     const int nkeys = min(TN, L - jt * TN);
     const T* kbase = khead + (int64_t)jt * TN * ks.s;
+#pragma unroll 4
     for (int i = threadIdx.x; i < TN * cpr; i += blockDim.x) {
-      const int r = i / cpr, c = i % cpr;
+      const int r = i / cpr, c = i % cpr;                  // shifts when head_dim is a compile-time constant
       const uint32_t dst = (uint32_t)__cvta_generic_to_shared(Ks + (buf * TN + r) * ld + c * 8);
       const T* src = kbase + (int64_t)min(r, nkeys - 1) * ks.s + c * 8;
       const int bytes = r < nkeys ? 16 : 0;                // rows past the end are filled with zeros
@@ -293,6 +297,7 @@ score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
         for (int t = 0; t < 4; ++t) acc[j][t] = 0.f;
       const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(Qs + (r0 + warp * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
       const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(Kt + ((lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+#pragma unroll
       for (int d0 = 0; d0 < D; d0 += 16) {
         uint32_t a[4];
         ldmatrix_x4(a, q_addr + d0 * 2);
@@ -322,19 +327,28 @@ score_mma_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
           }
         if (PASS == 1) {
           float m = -CUDART_INF_F;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int t = 0; t < 2; ++t)
-              if (full || 8 * j + 2 * (lane & 3) + t < nkeys) m = fmaxf(m, y[2 * j + t]);
-          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-          m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
           float z = 0.f;
+          if (full) {                                      // the common case: no per-key bound checks
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+            for (int c = 0; c < 16; ++c) m = fmaxf(m, y[c]);
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
 #pragma unroll
-            for (int t = 0; t < 2; ++t)
-              if (full || 8 * j + 2 * (lane & 3) + t < nkeys) z += __expf(y[2 * j + t] - m);
+            for (int c = 0; c < 16; ++c) z += __expf(y[c] - m);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+              for (int t = 0; t < 2; ++t)
+                if (8 * j + 2 * (lane & 3) + t < nkeys) m = fmaxf(m, y[2 * j + t]);
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+              for (int t = 0; t < 2; ++t)
+                if (8 * j + 2 * (lane & 3) + t < nkeys) z += __expf(y[2 * j + t] - m);
+          }
           z += __shfl_xor_sync(0xffffffffu, z, 1);
           z += __shfl_xor_sync(0xffffffffu, z, 2);
           if (r < bs && (lane & 3) == 0) partials[((int64_t)bh * ntile + jt) * bs + r] = make_float2(m, z);
@@ -504,8 +518,15 @@ int run(const Dims& d, const void* q, Strides qs, const void* k, Strides ks, voi
   for (int pass = 1; pass <= 2; ++pass) {
     if constexpr (DT != PBS_FP32) {
       if (mma) {
-        auto kern = pass == 1 ? (fastdiv ? score_mma_kernel<DT, 1, true> : score_mma_kernel<DT, 1, false>)
-                              : (fastdiv ? score_mma_kernel<DT, 2, true> : score_mma_kernel<DT, 2, false>);
+        using Kern = void (*)(const T*, Strides, const T*, Strides, float2*, const float2*, float*, T*, int, int, int, int,
+                              int, int, int, int, float);
+        auto pick = [&](auto dh) -> Kern {
+          constexpr int DH = decltype(dh)::value;
+          return pass == 1 ? (fastdiv ? (Kern)score_mma_kernel<DT, 1, true, DH> : (Kern)score_mma_kernel<DT, 1, false, DH>)
+                           : (fastdiv ? (Kern)score_mma_kernel<DT, 2, true, DH> : (Kern)score_mma_kernel<DT, 2, false, DH>);
+        };
+        Kern kern = d.D == 128 ? pick(std::integral_constant<int, 128>{})
+                    : d.D == 64 ? pick(std::integral_constant<int, 64>{}) : pick(std::integral_constant<int, 0>{});
         const size_t smem = pass == 1 ? smem1 : smem2;
         if (smem > 48 * 1024) {
           cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -42,3 +42,30 @@ MEANPOOLING_CASES = {
     "meanpool_nothing_fp32": (Workload("meanpool_nothing_fp32", 1, 2, 2, 64, 1000, "fp32", 64, 64, 1.5, 1e4), 25,
                               {"force_select_first_block": False, "force_select_current_block": False}, 4),
 }
+
+
+# Rotary embedding (the step before the path): name -> (dtype, B, H, Hkv, S, D, theta, broadcast cos/sin over the batch)
+ROPE_CASES = {
+    "rope_bf16": ("bf16", 2, 3, 1, 77, 128, 5e5, False),
+    "rope_fp16": ("fp16", 1, 8, 2, 300, 64, 1e4, True),
+    "rope_fp32": ("fp32", 2, 2, 2, 33, 128, 1e6, True),
+}
+
+
+def rope_inputs(case):
+    """Seeded q, k in the layout the attention layer produces ((B, S, H*D) projections viewed as (B, H, S, D)) and
+    cos / sin tables (B or 1, S, D) of the same dtype, all on the CPU."""
+    import torch
+    dt, B, H, Hkv, S, D, theta, bcast = case
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    g = torch.Generator().manual_seed(1234 + S)
+    q = torch.randn(B, S, H * D, generator=g).to(dtype).view(B, S, H, D).transpose(1, 2)
+    k = torch.randn(B, S, Hkv * D, generator=g).to(dtype).view(B, S, Hkv, D).transpose(1, 2)
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    pos = torch.arange(S, dtype=torch.float32) + 3.0 * torch.arange(B, dtype=torch.float32)[:, None]
+    ang = pos[..., None] * inv
+    emb = torch.cat([ang, ang], dim=-1)
+    cos, sin = emb.cos().to(dtype), emb.sin().to(dtype)
+    if bcast:
+        cos, sin = cos[:1], sin[:1]
+    return q, k, cos, sin

@@ -3,7 +3,7 @@
 Run once, on a machine that has the reference checked out (it is imported from the
 directory named by the REFERENCE_ROOT environment variable and is not needed afterwards):
 
-    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [--meanpooling-only] [--only=case,case]
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py [--meanpooling-only] [--rope-only] [--only=case,case]
 
 Per case two runs are stored: ``*_ref`` from the reference as it is (its sorts
 are non-stable: the order of tied items is implementation defined) and
@@ -159,8 +159,35 @@ def make_meanpooling(make_qkv, cases):
               f"{np.array_equal(rec['mask_ref'], rec['mask_stable'])}")
 
 
+def make_rope():
+    """Rotary-embedding fixture: the reference's own apply_rotary_pos_emb (pbs_attn/patch/huggingface.py:19-25)
+    on seeded inputs in the layout its attention layer produces, for the three dtypes."""
+    sys.path.insert(0, REFERENCE_ROOT)
+    try:
+        for name in [m for m in sys.modules if m == "pbs_attn" or m.startswith("pbs_attn.")]:
+            del sys.modules[name]
+        import pbs_attn.patch.huggingface as ref_hf
+        assert os.path.abspath(ref_hf.__file__).startswith(os.path.abspath(REFERENCE_ROOT)), ref_hf.__file__
+    finally:
+        sys.path.remove(REFERENCE_ROOT)
+    sys.path.insert(0, HERE)
+    from cases import ROPE_CASES, rope_inputs
+    rec = {}
+    for name, case in ROPE_CASES.items():
+        q, k, cos, sin = rope_inputs(case)
+        qe, ke = ref_hf.apply_rotary_pos_emb(q, k, cos, sin)
+        rec[f"{name}_q"], rec[f"{name}_k"] = raw(qe), raw(ke)
+        rec[f"{name}_sha"] = np.array(sha_inputs(q, k, cos, sin))
+    path = os.path.join(HERE, "rope.npz")
+    np.savez_compressed(path, **rec)
+    print(f"rope: {os.path.getsize(path) / 1024:.0f} KiB, {len(ROPE_CASES)} cases")
+
+
 def main():
     sys.path.insert(0, ROOT)
+    if "--rope-only" in sys.argv:
+        make_rope()
+        return
     from pbs_attn_b200.synth import make_qkv
     sys.path.insert(0, HERE)
     from cases import CASES, MEANPOOLING_CASES
@@ -170,6 +197,7 @@ def main():
         make_meanpooling(make_qkv, MEANPOOLING_CASES)
         return
     make_meanpooling(make_qkv, MEANPOOLING_CASES)
+    make_rope()
     for name, (w, seed, kwargs, stride) in CASES.items():
         q, k, v = make_qkv(w, seed)
         rec = {"inputs_sha256": np.array(sha_inputs(q, k, v)), "row_stride": np.array(stride)}

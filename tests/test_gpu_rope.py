@@ -33,6 +33,27 @@ def test_rope_kernel_is_bit_exact(dtype, B, H, Hkv, S, D, bcast):
     assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
 
 
+@pytest.mark.parametrize("name", ["rope_bf16", "rope_fp16", "rope_fp32"])
+def test_rope_kernel_equals_the_reference_fixture(name):
+    """Against outputs of the reference's own apply_rotary_pos_emb (tests/golden/rope.npz, made by
+    tests/golden/make_golden.py from the unmodified reference): bit-exact."""
+    import hashlib
+    import os
+    import numpy as np
+    from cases import ROPE_CASES, rope_inputs
+    from pbs_attn_b200.prefill import apply_rope_
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rope.npz"))
+    q, k, cos, sin = rope_inputs(ROPE_CASES[name])
+    h = hashlib.sha256()
+    for t in (q, k, cos, sin):
+        h.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+    assert h.hexdigest() == str(g[f"{name}_sha"]), "seeded inputs drifted from the ones the fixture was made from"
+    for x, want in ((q, g[f"{name}_q"]), (k, g[f"{name}_k"])):
+        got = apply_rope_(x.cuda().clone(memory_format=torch.preserve_format), cos.cuda(), sin.cuda()).cpu().contiguous()
+        raw = got.view(torch.int16).numpy().view(np.uint16) if got.dtype != torch.float32 else got.numpy()
+        assert np.array_equal(raw, want)
+
+
 def test_rope_rejects_bad_tables():
     from pbs_attn_b200.prefill import apply_rope_
     x = torch.zeros(1, 2, 16, 64, device="cuda", dtype=torch.bfloat16)

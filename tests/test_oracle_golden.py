@@ -89,3 +89,19 @@ def test_meanpooling_oracle_equals_reference(name):
     else:
         assert (r.block_mask & eye).sum() < eye.sum() * w.batch * w.q_heads     # ... an ordinary candidate otherwise
     assert not torch.triu(r.block_mask, diagonal=1).any()                        # nothing above it
+
+
+@pytest.mark.parametrize("name", ["rope_bf16", "rope_fp16", "rope_fp32"])
+def test_rotary_helper_equals_reference_fixture(name):
+    """The host-side rotary helper of the patch layer (used for CPU tensors and as the check of the CUDA
+    rotary kernel) against outputs of the reference's own function: bit-exact."""
+    import os
+    from cases import ROPE_CASES, rope_inputs
+    from pbs_attn.patch.huggingface import apply_rotary_pos_emb
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rope.npz"))
+    q, k, cos, sin = rope_inputs(ROPE_CASES[name])
+    qe, ke = apply_rotary_pos_emb(q, k, cos, sin)
+    for got, want in ((qe, g[f"{name}_q"]), (ke, g[f"{name}_k"])):
+        got = got.contiguous()
+        raw = got.view(torch.int16).numpy().view(np.uint16) if got.dtype != torch.float32 else got.numpy()
+        assert np.array_equal(raw, want)
