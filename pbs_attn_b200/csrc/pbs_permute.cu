@@ -6,9 +6,9 @@
 // the zero padding of pbs_attn/src/pbs.py:78-80 (key pooling) and pbs_attn/src/pbs.py:10-25.
 // Ties are broken towards the lower original position (a stable sort).
 //
-// One CTA per (segment, b, h).  HBM traffic per (b, h): importance read (4*L), K and V rows read
-// (served from L2 for the Hq/Hkv heads that share a KV head) and written once each (2*S*D*e),
-// indices written (4*S), pooled K written (nb*D*e).
+// One CTA per (segment, b, h); the heads of a KV group are adjacent in the grid.  HBM traffic per (b, h):
+// importance read (4*L), K and V rows read (from L2 for all but one of the Hq/Hkv heads that share a KV
+// head) and written once each (2*S*D*e), indices written (4*S), pooled K written (nb*D*e).
 #include "pbs_common.cuh"
 
 namespace pbs {
@@ -30,9 +30,12 @@ segment_permute_kernel(const float* __restrict__ importance,
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw);
   int32_t* order = reinterpret_cast<int32_t*>(keys + npow2);   // original position of each slot
 
-  const int sg = blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / Hq, h = bh % Hq;
+  // the query heads of a KV group sit next to each other in the grid: they gather the same K/V rows,
+  // which then come from HBM once and from L2 for the others
+  const int sg = blockIdx.x / group, hin = blockIdx.x % group;
+  const int Hkv = Hq / group;
+  const int b = blockIdx.y / Hkv, h = (blockIdx.y % Hkv) * group + hin;
+  const int bh = b * Hq + h;
   const int seg0 = sg * seg;
   const int n = min(seg, S - seg0);        // rows of this segment (the tail segment is shorter)
   const int L = nseg * seg;
@@ -100,6 +103,9 @@ segment_permute_kernel(const float* __restrict__ importance,
   }
 }
 
+// One CTA per (q block, b, h).  A thread owns one 16-row group x one 16-byte piece of the row: its 16
+// loads are independent (all in flight at once), its sums follow the reference's reduction order (rows
+// one after the other inside a group of 16); a second step adds the group sums in order.
 template <int DT>
 __global__ void __launch_bounds__(256)
 pool_queries_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
@@ -107,20 +113,46 @@ pool_queries_kernel(const typename Elem<DT>::T* __restrict__ q, Strides qs,
                     int Hq, int S, int D, int bs, int nb) {
   using E = Elem<DT>;
   using T = typename E::T;
+  constexpr int EPV = 16 / (int)sizeof(T);
+  __shared__ float part[16 * 256];                         // [16-row group][dim]
   const int blk = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh % Hq;
   const T* qb = q + (int64_t)b * qs.b + (int64_t)h * qs.h;
   const int r0 = blk * bs, r1 = min(r0 + bs, S);
+  const int groups = bs / 16, cpr = D / EPV;
+  const bool mean = pool_mode == PBS_POOL_MEAN;
+  for (int i = threadIdx.x; i < groups * cpr; i += blockDim.x) {
+    const int g = i / cpr, c = i % cpr;
+    const int g0 = r0 + 16 * g, n = max(0, min(16, r1 - g0));
+    uint4 raw[16];
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr)
+      if (rr < n) raw[rr] = *reinterpret_cast<const uint4*>(qb + (int64_t)(g0 + rr) * qs.s + c * EPV);
+    float acc[EPV];
+#pragma unroll
+    for (int t = 0; t < EPV; ++t) acc[t] = mean ? 0.f : -CUDART_INF_F;
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) {
+      if (rr < n) {
+        const T* e = reinterpret_cast<const T*>(&raw[rr]);
+#pragma unroll
+        for (int t = 0; t < EPV; ++t) acc[t] = mean ? acc[t] + E::ld(e + t) : fmaxf(acc[t], E::ld(e + t));
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < EPV; ++t) part[g * D + c * EPV + t] = acc[t];
+  }
+  __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float res;
-    if (pool_mode == PBS_POOL_MEAN) {
-      CascadeSum sum;
-      for (int r = r0; r < r1; ++r) sum.add(E::ld(qb + (int64_t)r * qs.s + d));
-      res = sum.total() / (float)bs;
+    if (mean) {
+      float a1 = 0.f;
+      for (int g = 0; g < groups; ++g) a1 += part[g * D + d];
+      res = a1 / (float)bs;
     } else {
-      float m = (r1 - r0 < bs) ? 0.f : -CUDART_INF_F;
-      for (int r = r0; r < r1; ++r) m = fmaxf(m, E::ld(qb + (int64_t)r * qs.s + d));
+      float m = (r1 - r0 < bs) ? 0.f : -CUDART_INF_F;     // zero padding takes part in the max
+      for (int g = 0; g < groups; ++g) m = fmaxf(m, part[g * D + d]);
       res = m;
     }
     pooled_q[((int64_t)bh * nb + blk) * D + d] = E::cvt(res);
@@ -140,7 +172,7 @@ int run_permute(const Dims& d, const float* importance, const void* k, Strides k
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e, "segment_permute_kernel smem attribute");
   }
-  kern<<<dim3(nsegs_all, d.B * d.Hq), 256, smem, st>>>(
+  kern<<<dim3(nsegs_all * d.group, d.B * d.Hkv), 256, smem, st>>>(
       importance, (const T*)k, ks, (const T*)v, vs, idx, (T*)perm_k, (T*)perm_v, (T*)pooled_k, pool_mode,
       first_block, d.Hq, d.group, d.S, d.D, d.bs, d.seg, d.nseg, d.nb, npow2);
   PBS_CUDA_CHECK_LAUNCH("segment_permute_kernel");
