@@ -347,3 +347,46 @@ def test_output_replicas_receive_the_same_bytes():
     with pytest.raises(_cabi.PbsError, match="replicas"):
         permuted_block_sparse_attn_fwd(qd, kd, vd, w.block_size, w.segment_size, w.threshold, True,
                                        attn_impl="simt", out=out_view, out_replicas=rep)
+
+
+@pytest.mark.parametrize("dt,D,S,bs,seg,diag", [
+    ("fp32", 128, 4096, 64, 256, False),      # 32 pieces per pooled row
+    ("fp16", 64, 8192, 64, 128, False),       # 8 pieces per pooled row
+    ("bf16", 128, 131072, 64, 512, False),    # 2048 blocks per row: 64 blocks per lane
+    ("bf16", 128, 20000, 128, 128, True),     # MeanPooling flavour: diagonal candidates, ragged length
+    ("fp32", 64, 3000, 16, 64, False),        # small blocks
+])
+def test_tiled_selection_kernel_equals_general_kernel_on_random_pooled_rows(dt, D, S, bs, seg, diag):
+    """The two selection kernels on random pooled rows written straight into the plan's buffers (shapes the
+    fixtures do not reach: wide fp32 rows, 2048 blocks per row, diagonal candidates), including tie-heavy
+    rows (few distinct pooled keys) and a per-head threshold."""
+    from pbs_attn_b200 import _cabi
+    from pbs_attn_b200.prefill import Plan
+    from pbs_attn_b200.synth import Workload
+    lib = _cabi.load()
+    w = Workload("rand", 1, 3, 1, D, S, dt, bs, seg, 0.9, 1e4)
+    plan = Plan(w.batch, w.q_heads, w.kv_heads, S, D, bs, seg, w.torch_dtype, torch.device("cuda"))
+    g = torch.Generator(device="cuda").manual_seed(S + D)
+    nb = plan.nb
+    for ties in (False, True):
+        pq = torch.randn(1, 3, nb, D, generator=g, device="cuda")
+        pk = torch.randn(1, 3, nb, D, generator=g, device="cuda")
+        if ties:                                   # many equal pooled keys -> equal scores -> cuts through tie groups
+            pk = pk[:, :, torch.randint(0, 7, (nb,), generator=g, device="cuda")]
+        plan.pooled_q.copy_(pq.to(w.torch_dtype))
+        plan.pooled_k.copy_(pk.to(w.torch_dtype))
+        plan.first_block.copy_(torch.randint(0, nb, (plan.first_block.numel(),), generator=g, device="cuda", dtype=torch.int32))
+        for thr in (0.9, 0.3, torch.tensor([0.5, 0.99, 0.0])):
+            opt = plan.options(thr, True, diagonal_candidates=diag, no_permutation=diag)
+            got = {}
+            try:
+                for impl in (0, 1):
+                    assert lib.pbs_debug_set_select_impl(impl) == 0
+                    scores = plan.select_blocks(opt, want_scores=True)
+                    torch.cuda.synchronize()
+                    got[impl] = (plan.block_mask.clone(), scores.clone())
+            finally:
+                lib.pbs_debug_set_select_impl(0)
+            nd = (got[0][0] != got[1][0]).sum().item()
+            assert nd == 0, f"ties={ties} thr={thr}: masks differ in {nd} bits"
+            assert torch.equal(got[0][1], got[1][1]), f"ties={ties} thr={thr}: pooled scores differ"
