@@ -286,7 +286,9 @@ struct Smem {
   static constexpr int kK = kQ + 2 * kTileBytes;          // NK tiles
   static constexpr int kV = kK + NK * kTileBytes;         // NV tiles
   static constexpr int kIdx = kV + NV * kTileBytes;       // 8 warps x 128 int32
-  static constexpr int kBars = kIdx + 8 * 128 * 4;
+  static constexpr int kStage = kIdx + 8 * 128 * 4;       // 8 warps x 32 rows x (64 + 16) bytes: epilogue transposition
+  static constexpr int kStageRow = 80;                    // bytes per staged row piece (64 of data + 16 of padding)
+  static constexpr int kBars = kStage + 8 * 32 * kStageRow;
   static constexpr int kCtl = kBars + (int)sizeof(Bars);
   static constexpr int kTotal = kCtl + (int)sizeof(Ctl) + 1024;   // + slack for 1024-byte alignment
 };
@@ -660,33 +662,47 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
       }
+      // Rows leave through a per-warp transposition tile: a thread owns one row of O in TMEM, but four
+      // lanes then store one row's 64-byte piece together, so a store instruction writes 8 rows x 64
+      // contiguous bytes instead of 32 rows x 16 -- this matters for the replicas, which travel over NVLink.
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int64_t ooff = (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)qpos * p.os.s;
-      T* orow = reinterpret_cast<T*>(p.out) + ooff;
+      unsigned char* stage = smem + SM::kStage + (warp - 4) * 32 * SM::kStageRow;
+      const int64_t obase = (int64_t)b * p.os.b + (int64_t)h * p.os.h;
+      const int wrow0 = r0 + wq * 32;                      // first query row of this warp
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        uint32_t o[16];
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
         if (steps > 0) {
-          tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
+          tmem_ld32(tmem_O[i] + lane_off + c * 32, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) o[j] = 0u;
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
         }
-        if (qpos < p.S) {
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            uint4 w;
-            w.x = PackP<DT>::pack(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
-            w.y = PackP<DT>::pack(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
-            w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
-            w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-            __stcs(reinterpret_cast<uint4*>(orow + c * 16 + j * 8), w);   // written once, not re-read here
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = PackP<DT>::pack(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+          w.y = PackP<DT>::pack(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+          w.z = PackP<DT>::pack(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+          w.w = PackP<DT>::pack(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * SM::kStageRow + j * 16) = w;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = (lane >> 2) + 8 * j, piece = lane & 3;
+          const int grow = wrow0 + rr;
+          if (grow < p.S) {
+            const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * SM::kStageRow + piece * 16);
+            const int64_t off = obase + (int64_t)grow * p.os.s + c * 32 + piece * 8;
+            __stcs(reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + off), w);   // written once, not re-read here
             // replicas (peer GPUs of a head-sharded call): plain stores, they travel over NVLink
             for (int x = 0; x < p.n_extra; ++x)
-              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.extra_out[x]) + ooff + c * 16 + j * 8) = w;
+              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.extra_out[x]) + off) = w;
           }
         }
+        __syncwarp();
       }
       // the next item's first P V overwrites O_i: order our TMEM reads before the arrive that lets it go
       tc_fence_before();

@@ -372,14 +372,15 @@ def MeanPooling_prefill(
     candidates.  With ``force_select_current_block=False`` the q block's own kv block is an ordinary
     candidate (MeanPooling.py:55-58 skipped): a q block that does not select it does not attend it,
     and a q block that selects nothing outputs zeros.  Additive: batch > 1 and Hkv < Hq are accepted.
-    ``causal=False`` is not supported (the attention kernels are causal).
+    ``causal=False`` fails with the reference's own assertion: its ``select_blocks`` only supports
+    causal selection (pbs_attn/src/utils.py:54), so the baseline never ran non-causally there either.
     """
     batch_size, num_q_heads, q_len, head_dim = query_states.shape
     _, num_kv_heads, kv_len, _ = key_states.shape
     assert num_q_heads % num_kv_heads == 0
     assert q_len == kv_len, "Only support prefilling for now, q_len: {}, kv_len: {}".format(q_len, kv_len)
-    if not causal:
-        raise NotImplementedError("MeanPooling_prefill on the CUDA library is causal")
+    # the reference accepts causal=False here but then fails in select_blocks (pbs_attn/src/utils.py:54)
+    assert causal == True, "This implementation variant strictly supports causal=True."  # noqa: E712
     if not query_states.is_cuda:
         raise RuntimeError("pbs_attn_b200 runs on CUDA devices only; there is no CPU path")
     q = _readable(query_states, need_distinct_heads=True)

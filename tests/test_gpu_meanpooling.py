@@ -94,6 +94,6 @@ def test_meanpooling_factory_and_patch_probe():
     fn = get_meanpooling_prefill(block_size=64, threshold=0.8)
     assert isinstance(fn, partial) and fn.func is MeanPooling_prefill
     assert "layer_idx" not in fn.func.__code__.co_varnames
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(AssertionError, match="causal=True"):      # the reference's select_blocks asserts the same
         MeanPooling_prefill(torch.zeros(1, 1, 128, 64, device="cuda"), torch.zeros(1, 1, 128, 64, device="cuda"),
                             torch.zeros(1, 1, 128, 64, device="cuda"), causal=False)
