@@ -193,6 +193,28 @@ __device__ __forceinline__ float ex2(float x) {
   return r;
 }
 
+// 2^x for a pair on the FMA pipe instead of the special-function unit: floor by the magic-number
+// addition (round down), then a cubic on the fraction (relative error 8.6e-5, below the rounding of P
+// to 16 bits) and the integer part added into the exponent field.  x <= -127 gives exactly 0.
+__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
+  const float2 xc = make_float2(fmaxf(x.x, -127.f), fmaxf(x.y, -127.f));
+  const float2 t = __fadd2_rd(xc, make_float2(12582912.f, 12582912.f));
+  const float2 fl = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(fl, make_float2(-1.f, -1.f), xc);
+  float2 r = __ffma2_rn(make_float2(0.07706724f, 0.07706724f), f, make_float2(0.22764498f, 0.22764498f));
+  r = __ffma2_rn(r, f, make_float2(0.69511664f, 0.69511664f));
+  r = __ffma2_rn(r, f, make_float2(1.f, 1.f));
+  return make_float2(__uint_as_float(__float_as_uint(r.x) + (__float_as_uint(t.x) << 23)),
+                     __uint_as_float(__float_as_uint(r.y) + (__float_as_uint(t.y) << 23)));
+}
+
+#ifndef PBS_POLY_EVERY
+#define PBS_POLY_EVERY 0
+#endif
+#ifndef PBS_SETMAXNREG
+#define PBS_SETMAXNREG 0
+#endif
+
 template <int DT> struct PackP;
 template <> struct PackP<PBS_BF16> {
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
@@ -346,6 +368,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   constexpr uint32_t kIdescQK = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);   // N = 64
   constexpr uint32_t kIdescPV = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (1u << 16) | (((uint32_t)D >> 3) << 17) | ((128u >> 4) << 24);
 
+
+#if PBS_SETMAXNREG
+  // The softmax warps hold a half-step of S in registers; the four warps of the other roles need few.
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PBS_SETMAXNREG));
+  else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(((64512 - 128 * PBS_SETMAXNREG) / 256) & ~7));
+#endif
 
   if (warp == 0) {
     // =========================================================================== TMA producer
@@ -591,57 +619,71 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
             for (int c = 0; c < 64; ++c) v[c] = -CUDART_INF_F;
           }
-          float mx[2];
+          // Row maximum (four independent chains) and, without waiting for it, the exponentials relative to
+          // the maximum in use: the lazy rescale keeps that maximum for almost every half-step, so the chain
+          // of maxima leaves the critical path.  When a row's maximum did grow past the threshold (always in
+          // a row's first half-step) the warp rescales and exponentiates again.
+          float mx4[4];
 #pragma unroll
-          for (int a = 0; a < 2; ++a) {
-            float m = max3(v[32 * a], v[32 * a + 1], v[32 * a + 2]);
+          for (int a = 0; a < 4; ++a) {
+            float m = max3(v[16 * a], v[16 * a + 1], v[16 * a + 2]);
 #pragma unroll
-            for (int c = 3; c + 1 < 32; c += 2) m = max3(m, v[32 * a + c], v[32 * a + c + 1]);
-            mx[a] = fmaxf(m, v[32 * a + 31]);
+            for (int c = 3; c + 1 < 16; c += 2) m = max3(m, v[16 * a + c], v[16 * a + c + 1]);
+            mx4[a] = fmaxf(m, v[16 * a + 15]);
           }
-          const float mt = fmaxf(mx[0], mx[1]) * p.scale_log2e;
-
-          float alpha = 1.f;
-          if (mt > m_used + kRescaleThreshold) {           // also the first finite maximum
-            alpha = ex2(m_used - mt);                      // 0 when m_used is -inf
-            m_used = mt;
-            l *= alpha;
-          }
-          const bool rescale = (steps > 0 || hs == 1) && __any_sync(0xffffffffu, alpha != 1.f);
-          if (rescale) {
-            // O_i holds the sum up to the previous half-step: wait for that P V, then scale in place.
-            // Half 0 follows the second half of the previous entry, half 1 the first half of this one.
-            const uint32_t par = hs == 0 ? ((sc - 1u) & 1u) : (sc & 1u);
-            ok = __all_sync(0xffffffffu, wait_bar(bar_o[hs ^ 1], par, ctl, p.status, 10));
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D / 16; ++c) {
-              uint32_t o[16];
-              tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-              tmem_st16(tmem_O[i] + lane_off + c * 16, o);
-            }
-          }
-          const float m_eff = (m_used == -CUDART_INF_F) ? 0.f : m_used;
           const float2 sc2 = make_float2(p.scale_log2e, p.scale_log2e);
-          const float2 nm2 = make_float2(-m_eff, -m_eff);
-          float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+          float2 acc2[2];
           // P_h goes back over the first 32 columns of S_h in two stores of 32 keys
-          uint32_t pk[16];
+          auto exp_pass = [&](float m_ref) {
+            const float2 nm2 = make_float2(-m_ref, -m_ref);
+            acc2[0] = make_float2(0.f, 0.f);
+            acc2[1] = make_float2(0.f, 0.f);
+            uint32_t pk[16];
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
+            for (int q = 0; q < 2; ++q) {
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int col = 32 * q + 2 * c;
-              const float2 x = __ffma2_rn(make_float2(v[col], v[col + 1]), sc2, nm2);
-              const float2 ex = make_float2(ex2(x.x), ex2(x.y));
-              acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
-              pk[c] = PackP<DT>::pack(ex.x, ex.y);
+              for (int c = 0; c < 16; ++c) {
+                const int col = 32 * q + 2 * c;
+                const float2 x = __ffma2_rn(make_float2(v[col], v[col + 1]), sc2, nm2);
+                float2 ex;
+                if (PBS_POLY_EVERY > 0 && (16 * q + c) % (PBS_POLY_EVERY > 0 ? PBS_POLY_EVERY : 1) == PBS_POLY_EVERY - 1)
+                  ex = exp2_fma_pipe(x);
+                else
+                  ex = make_float2(ex2(x.x), ex2(x.y));
+                acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
+                pk[c] = PackP<DT>::pack(ex.x, ex.y);
+              }
+              tmem_st16(s_addr + 16 * q, pk);
             }
-            tmem_st16(s_addr + 16 * q, pk);
+          };
+          exp_pass(m_used == -CUDART_INF_F ? 0.f : m_used);
+          const float mt = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;
+          const bool grew = mt > m_used + kRescaleThreshold;   // also the first finite maximum
+          if (__any_sync(0xffffffffu, grew)) {
+            float alpha = 1.f;
+            if (grew) {
+              alpha = ex2(m_used - mt);                      // 0 when m_used is -inf
+              m_used = mt;
+              l *= alpha;
+            }
+            if (steps > 0 || hs == 1) {
+              // O_i holds the sum up to the previous half-step: wait for that P V, then scale in place.
+              // Half 0 follows the second half of the previous entry, half 1 the first half of this one.
+              const uint32_t par = hs == 0 ? ((sc - 1u) & 1u) : (sc & 1u);
+              ok = __all_sync(0xffffffffu, wait_bar(bar_o[hs ^ 1], par, ctl, p.status, 10));
+              if (!ok) break;
+              tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < D / 16; ++c) {
+                uint32_t o[16];
+                tmem_ld16(tmem_O[i] + lane_off + c * 16, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                tmem_st16(tmem_O[i] + lane_off + c * 16, o);
+              }
+            }
+            exp_pass(m_used == -CUDART_INF_F ? 0.f : m_used);
           }
           tmem_wait_st();
           tc_fence_before();
