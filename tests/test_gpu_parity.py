@@ -390,3 +390,33 @@ def test_tiled_selection_kernel_equals_general_kernel_on_random_pooled_rows(dt, 
             nd = (got[0][0] != got[1][0]).sum().item()
             assert nd == 0, f"ties={ties} thr={thr}: masks differ in {nd} bits"
             assert torch.equal(got[0][1], got[1][1]), f"ties={ties} thr={thr}: pooled scores differ"
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+@pytest.mark.parametrize("step_keys", [64, 128])
+def test_attention_when_the_row_maximum_keeps_growing(impl, step_keys):
+    """Scores that rise by ~12 (log2 units) every 64 or 128 keys: the running maximum of every row
+    outgrows the lazy-rescale threshold in (almost) every half-step, so the kernel takes its slow path
+    -- rescale the output accumulator, exponentiate again -- all the way.  Every causal block is selected
+    (integer threshold 1); the result is compared with plain fp32 causal attention on the same 16-bit inputs
+    (the kernels accumulate Q K^T in fp32 like the reference's Triton kernel; the CPU oracle follows the
+    reference's torch path, which rounds these large scores to 16 bits and is therefore not the yardstick here)."""
+    from pbs_attn_b200.prefill import permuted_block_sparse_attn_fwd
+    B, Hq, Hkv, S, D = 1, 2, 1, 2048, 128
+    g = torch.Generator().manual_seed(11)
+    u = torch.ones(D) / D ** 0.5
+    level = (torch.arange(S) // step_keys).float() * 100.0
+    q = (u[None, :] + 0.05 * torch.randn(S, D, generator=g)).expand(B, Hq, S, D).contiguous()
+    k = (level[:, None] * u[None, :] + 0.5 * torch.randn(S, D, generator=g)).expand(B, Hkv, S, D).contiguous()
+    v = 0.5 * torch.randn(B, Hkv, S, D, generator=g)     # |out| < 2: its own bf16 rounding stays below 4e-3
+    q, k, v = [t.to(torch.bfloat16).cuda() for t in (q, k, v)]
+    inter = {}
+    out = permuted_block_sparse_attn_fwd(q, k, v, 128, 256, 1, True, attn_impl=impl, intermediates=inter)
+    torch.cuda.synchronize()
+    inter["plan"].check_status()
+    assert bool(inter["block_mask"].bool().tril().sum() == inter["block_mask"].bool().sum())
+    s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float().repeat_interleave(Hq // Hkv, 1)) / D ** 0.5
+    s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device="cuda").triu(1), float("-inf"))
+    want = torch.softmax(s, -1) @ v.float().repeat_interleave(Hq // Hkv, 1)
+    d = (out.float() - want).abs()
+    assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3, (d.max().item(), d.mean().item())
