@@ -414,7 +414,8 @@ def test_attention_when_the_row_maximum_keeps_growing(impl, step_keys):
     out = permuted_block_sparse_attn_fwd(q, k, v, 128, 256, 1, True, attn_impl=impl, intermediates=inter)
     torch.cuda.synchronize()
     inter["plan"].check_status()
-    assert bool(inter["block_mask"].bool().tril().sum() == inter["block_mask"].bool().sum())
+    nb = S // 128
+    assert bool(inter["block_mask"].bool()[..., torch.ones(nb, nb, dtype=torch.bool).tril()].all()), "a causal block is off"
     s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float().repeat_interleave(Hq // Hkv, 1)) / D ** 0.5
     s = s.masked_fill(torch.ones(S, S, dtype=torch.bool, device="cuda").triu(1), float("-inf"))
     want = torch.softmax(s, -1) @ v.float().repeat_interleave(Hq // Hkv, 1)
