@@ -193,28 +193,6 @@ __device__ __forceinline__ float ex2(float x) {
   return r;
 }
 
-// 2^x for a pair on the FMA pipe instead of the special-function unit: floor by the magic-number
-// addition (round down), then a cubic on the fraction (relative error 8.6e-5, below the rounding of P
-// to 16 bits) and the integer part added into the exponent field.  x <= -127 gives exactly 0.
-__device__ __forceinline__ float2 exp2_fma_pipe(float2 x) {
-  const float2 xc = make_float2(fmaxf(x.x, -127.f), fmaxf(x.y, -127.f));
-  const float2 t = __fadd2_rd(xc, make_float2(12582912.f, 12582912.f));
-  const float2 fl = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
-  const float2 f = __ffma2_rn(fl, make_float2(-1.f, -1.f), xc);
-  float2 r = __ffma2_rn(make_float2(0.07706724f, 0.07706724f), f, make_float2(0.22764498f, 0.22764498f));
-  r = __ffma2_rn(r, f, make_float2(0.69511664f, 0.69511664f));
-  r = __ffma2_rn(r, f, make_float2(1.f, 1.f));
-  return make_float2(__uint_as_float(__float_as_uint(r.x) + (__float_as_uint(t.x) << 23)),
-                     __uint_as_float(__float_as_uint(r.y) + (__float_as_uint(t.y) << 23)));
-}
-
-#ifndef PBS_POLY_EVERY
-#define PBS_POLY_EVERY 0
-#endif
-#ifndef PBS_SETMAXNREG
-#define PBS_SETMAXNREG 0
-#endif
-
 template <int DT> struct PackP;
 template <> struct PackP<PBS_BF16> {
   static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
@@ -645,11 +623,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
               for (int c = 0; c < 16; ++c) {
                 const int col = 32 * q + 2 * c;
                 const float2 x = __ffma2_rn(make_float2(v[col], v[col + 1]), sc2, nm2);
-                float2 ex;
-                if (PBS_POLY_EVERY > 0 && (16 * q + c) % (PBS_POLY_EVERY > 0 ? PBS_POLY_EVERY : 1) == PBS_POLY_EVERY - 1)
-                  ex = exp2_fma_pipe(x);
-                else
-                  ex = make_float2(ex2(x.x), ex2(x.y));
+                const float2 ex = make_float2(ex2(x.x), ex2(x.y));
                 acc2[c & 1] = __fadd2_rn(acc2[c & 1], ex);
                 pk[c] = PackP<DT>::pack(ex.x, ex.y);
               }
