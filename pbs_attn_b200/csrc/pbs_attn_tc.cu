@@ -14,9 +14,11 @@
 //               their own 64 TMEM columns: S_h = Q K_h^T (SS, both operands K-major, 128B swizzle,
 //               M=128 N=64) and O += P_h V_h (TS: P_h read from TMEM, V MN-major from shared memory)
 //   warp 2      owns the TMEM allocation (all 512 columns: per query tile S_0 S_1 (64 each) and O (128))
-//   warps 4-7   softmax of query tile 0: per half-step tcgen05.ld S_h, mask, row max / exp2 / row
-//   warps 8-11  softmax of query tile 1  sum, P_h written back over the first 32 columns of S_h as
-//               packed 16-bit pairs; lazy rescale of O in TMEM; final O / l epilogue to global
+//   warps 4-7   softmax of query tile 0: per half-step tcgen05.ld S_h, mask, exp2 relative to the row
+//   warps 8-11  softmax of query tile 1  maximum in use (the new maximum is computed beside it and only a
+//               row that outgrew the lazy-rescale threshold makes the warp rescale O in TMEM and start
+//               over), row sum, P_h written back over the first 32 columns of S_h as packed 16-bit
+//               pairs; final O / l epilogue to global through a per-warp transposition tile
 // An issuer runs, per list entry and half h: O += P_h V_h, then S_h of the next entry into the
 // columns P_h vacated.  So while a softmax warpgroup works on one half, the MMAs of the other half
 // (and of the other query tile) run, and the next S is ready when the warpgroup comes back for it.
